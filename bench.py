@@ -1,0 +1,354 @@
+"""MoE-layer throughput benchmark.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c2]
+
+One step = one pass of the MoE block over one batch of synthetic tokens.
+At N=1 the workload is the Qwen3.5-MoE-shaped decode step (64 tokens, hidden
+2048, 256 experts, top-8, intermediate 512, shared expert, affine 4-bit g64,
+seed 0).  Prints ONE JSON line (rank 0).
+
+  value     tokens/s with the tokens already resident in HBM (CUDA events
+            around the K timed steps, max over ranks)
+  e2e       tokens/s through the host-buffer entry point: pinned host
+            activations in, pinned host result out, copies inside the timed
+            region
+  roofline  the first expert product (gate/up + SwiGLU), the kernel that moves
+            the most bytes: algorithmic bytes per launch / its average
+            duration from CUDA events recorded around it on its stream
+  cpu_baseline  the CPU restatement of the reference's algorithm timed on this
+            host's cores on a bounded sample (rank 0, N=1 only)
+
+--impl reference times that CPU restatement alone (the reference's own MLX
+backend cannot be built here: MLX is not in its tree).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_tokens_per_sec"
+UNIT = "tokens/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="c2")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the
+    timed region runs (read-only queries)."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "hw_power_brake": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = get(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def workload_desc(cfg, extra=None):
+    d = {"workload": f"{cfg.name}: {cfg.tokens} tokens, hidden {cfg.hidden}, {cfg.num_experts} experts top-{cfg.top_k}, "
+                     f"intermediate {cfg.intermediate}, shared {cfg.shared_intermediate}, "
+                     f"{cfg.mode} {cfg.bits}-bit g{cfg.group_size}, seed {cfg.seed}",
+         "l2": "weights streamed per step (453 MB) exceed the 126 MB L2; no flush needed"}
+    if extra:
+        d.update(extra)
+    return d
+
+
+# ── CPU baseline: the checker's restatement of the reference algorithm ───────
+def cpu_baseline(cfg, moe_host_params, x, seconds):
+    """Times oracle.moe.moe_forward on a bounded sample: as many whole steps of
+    the same workload as fit the budget (at least one)."""
+    from oracle import moe as O
+    t0 = time.perf_counter()
+    steps = 0
+    while True:
+        O.moe_forward(x, moe_host_params, fast_bucket=True)
+        steps += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds or steps >= 50:
+            break
+    import numpy as np
+    try:
+        from threadpoolctl import threadpool_info
+        cores = max([p.get("num_threads", 1) for p in threadpool_info()] + [1])
+    except Exception:
+        cores = 1
+    return {"value": cfg.tokens * steps / dt, "unit": UNIT, "cores": int(cores), "kind": "port",
+            "sample": f"{steps} full step(s) of {cfg.name} in {dt:.1f} s with the numpy checker "
+                      f"(per-expert loop, fp32/float64 accumulate)"}
+
+
+def host_params_from_device(moe, cfg):
+    """Checker-side parameters holding the very bytes the GPU uses."""
+    import numpy as np
+    from oracle import formats as F
+    from oracle import moe as O
+
+    def q(ql):
+        w = ql.weight.cpu().numpy().view(np.uint32)
+        if ql.mode == "affine":
+            s = ql.scales.view(__import__("torch").int16).cpu().numpy().view(F.bf16)
+            b = ql.biases.view(__import__("torch").int16).cpu().numpy().view(F.bf16)
+        else:
+            s, b = ql.scales.cpu().numpy(), None
+        return O.QLinear(w, s, b, ql.group_size, ql.bits, ql.mode, ql.global_scale)
+
+    import torch
+    p = O.MoEParams(router_w=moe.gate.weight.float().cpu().numpy().astype(F.bf16),
+                    gate_up=q(moe._fused.gate_up), down=q(moe._fused.down),
+                    num_experts_per_tok=cfg.top_k, norm_topk_prob=cfg.norm_topk_prob)
+    if moe.shared_expert is not None:
+        p.shared_gate_proj = q(moe.shared_expert.gate_proj)
+        p.shared_up_proj = q(moe.shared_expert.up_proj)
+        p.shared_down_proj = q(moe.shared_expert.down_proj)
+        p.shared_expert_gate_w = moe.shared_expert_gate.weight.float().cpu().numpy().astype(F.bf16)
+    if moe.router_logit_bias is not None:
+        p.router_logit_bias = moe.router_logit_bias.cpu().numpy()
+    return p
+
+
+def run_reference(args):
+    """The reference arm: the CPU restatement on this host's cores (rank 0 only)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from ironmlx_b200.workloads import CONFIGS, Workload
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from util import make_params
+    cfg = CONFIGS[args.config]
+    # bounded sample: the same layer shape and tokens, over the experts of a
+    # 32-expert slice (each step then costs seconds, not minutes, of numpy)
+    sample = cfg.with_(name=cfg.name + "-e32", num_experts=min(cfg.num_experts, 32))
+    x, p = make_params(sample)
+    from oracle import moe as O
+    for _ in range(min(args.warmup, 1)):
+        O.moe_forward(x, p, fast_bucket=True)
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        O.moe_forward(x, p, fast_bucket=True)
+    dt = time.perf_counter() - t0
+    val = sample.tokens * steps / dt
+    try:
+        from threadpoolctl import threadpool_info
+        cores = max([q.get("num_threads", 1) for q in threadpool_info()] + [1])
+    except Exception:
+        cores = 1
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 1), "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_desc(cfg, {"sample": f"{sample.num_experts} of {cfg.num_experts} experts"}),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": int(cores), "kind": "port",
+                         "sample": f"{steps} step(s) of {sample.name} with the numpy checker"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference's MLX backend is not buildable here (MLX absent from its tree, no Rust toolchain); "
+                "this is the CPU restatement of its algorithm",
+    }
+    print(json.dumps(line))
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from ironmlx_b200 import synthetic
+    from ironmlx_b200.workloads import CONFIGS, Workload, algorithmic_bytes_decode
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = CONFIGS[args.config]
+    wl = Workload(cfg)
+
+    if world > 1:
+        from ironmlx_b200 import ep
+        runner = ep.build_bench_runner(cfg, dev, rank, world)
+    else:
+        moe = synthetic.build_moe(cfg, dev)
+        x = torch.from_numpy(wl.activations()).to(dev).to(torch.bfloat16)
+        runner = None
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput ----
+    step = (lambda: moe.forward_with_stream(x)) if runner is None else runner.step
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            step()
+        end.record()
+        barrier()
+    ms = start.elapsed_time(end) / args.steps
+    t = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    tokens_per_step = cfg.tokens * world
+    value = tokens_per_step / (ms * 1e-3)
+
+    # ---- end to end through the host-buffer entry point ----
+    if runner is None:
+        xh = x.cpu().pin_memory()
+        yh = torch.empty_like(xh).pin_memory()
+        e2e_step = lambda: moe.forward_host(xh, yh)
+    else:
+        e2e_step = runner.step_host
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_steps = max(10, args.steps // 10)
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
+    t = torch.tensor([e2e_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    io_bytes = cfg.tokens * cfg.hidden * 2
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+        "config": workload_desc(cfg, {"parallelism": f"ep{world}" if world > 1 else "single"}),
+        "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": io_bytes,
+                "d2h_bytes_per_step": io_bytes, "ms_per_step": e2e_ms},
+        "clocks": clocks.summary(),
+    }
+
+    if runner is None:
+        # ---- roofline of the dominant kernel, timed live with CUDA events ----
+        stage = np.zeros(5)
+        reps = 50
+        for _ in range(reps):
+            _, st = moe.forward_timed(x)
+            stage += np.array(st)
+        stage /= reps
+        _, tr = moe.forward_with_stream(x, trace=True)
+        touched = int((tr["counts"] > 0).sum().item())
+        per_w = cfg.bits / 8 + 4 / cfg.group_size if cfg.mode == "affine" else (1 + 1 / 32 if cfg.mode == "mxfp8" else 0.5 + 1 / 16)
+        gu_bytes = (touched * 2 * cfg.intermediate + 2 * cfg.shared_intermediate) * cfg.hidden * per_w
+        peak, which = peaks()
+        achieved = gu_bytes / (stage[2] * 1e-3) / 1e9
+        total_bytes = algorithmic_bytes_decode(cfg, touched)
+        line["roofline"] = {
+            "bound": "hbm", "kernel": "decode_mma_kernel<4,true> (gate/up + SwiGLU)", "achieved": achieved,
+            "peak": peak, "peak_source": f"of {which}", "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+            "algorithmic_bytes_per_launch": gu_bytes, "launch_ms": float(stage[2]),
+            "stage_ms": {"router": float(stage[0]), "sort": float(stage[1]), "gate_up": float(stage[2]),
+                         "down": float(stage[3]), "combine": float(stage[4])},
+            "layer": {"algorithmic_bytes": total_bytes, "touched_experts": touched,
+                      "achieved_gbs": total_bytes / (ms * 1e-3) / 1e9, "frac": total_bytes / (ms * 1e-3) / 1e9 / peak},
+        }
+        line["gpu_launches"] = 5 * args.steps
+        if rank == 0 and not args.no_cpu_baseline:
+            p = host_params_from_device(moe, cfg)
+            xs = wl.activations()
+            line["cpu_baseline"] = cpu_baseline(cfg, p, xs, args.cpu_seconds)
+    else:
+        line["gpu_launches"] = runner.launches_per_step * args.steps
+        line.update(runner.extra())
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,225 @@
+/* ironmlx_b200 — C ABI of the B200-native mixture-of-experts block.
+ *
+ * Drop-in boundary for the hot path of ironmlx's Qwen3.5-MoE model: the body
+ * of `MoEMLP::forward_with_stream` (mlx/src/nn/moe.rs:55-183) and the two
+ * quantized ops it is built from, `ops::quantized_matmul` and
+ * `ops::dequantize` (mlx/src/ops.rs:653-727), which the reference reaches
+ * through mlx-sys's bindgen of the mlx-c API.  A Rust `-sys` crate next to
+ * mlx-sys binds exactly these symbols.
+ *
+ * Conventions (they follow the mlx-c conventions the reference relies on,
+ * mlx/src/ops.rs:12-27, mlx/src/error.rs:17-54):
+ *   - every function returns int, 0 = success; on failure a message is kept
+ *     per thread and read with imx_last_error(); nothing aborts or exits;
+ *   - all pointers are DEVICE pointers unless the name says `host`;
+ *   - work is enqueued on the given cudaStream_t (passed as void*) and the
+ *     call returns without synchronising, except where stated;
+ *   - no call allocates device memory: scratch comes from the caller as a
+ *     workspace whose size imx_moe_workspace_bytes() reports;
+ *   - one caller thread per workspace (the reference runs one engine thread
+ *     per model, ironmlx/src/engine_pool.rs:79-81).
+ *
+ * Tensor formats (MLX's, see mlx/src/ops.rs:646-652,688-693):
+ *   activations  bf16 row-major [N, hidden]
+ *   dense weights bf16 row-major [out, in]
+ *   quantized     packed uint32 [.., out, in*bits/32] + scales (+ biases)
+ *                 [.., out, in/group]; affine: bf16 scales and biases;
+ *                 mxfp8: uint8 ue8m0 scales; nvfp4: uint8 e4m3 scales and one
+ *                 fp32 scale for the whole tensor.
+ */
+#ifndef IRONMLX_B200_H
+#define IRONMLX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define IMX_API __attribute__((visibility("default")))
+#else
+#define IMX_API
+#endif
+
+#define IMX_OK 0
+#define IMX_ERR_INVALID 1       /* bad argument / unsupported shape          */
+#define IMX_ERR_CUDA 2          /* a CUDA runtime call failed                */
+#define IMX_ERR_WORKSPACE 3     /* workspace too small or misaligned         */
+#define IMX_ERR_DEVICE 4        /* a kernel recorded an error status         */
+
+#define IMX_MODE_AFFINE 0
+#define IMX_MODE_MXFP8 1
+#define IMX_MODE_NVFP4 2
+
+/* Execution path of the expert products.  AUTO picks by tokens per expert. */
+#define IMX_PATH_AUTO 0
+#define IMX_PATH_DECODE 1       /* grouped dequant small-N tensor-core kernel */
+#define IMX_PATH_PREFILL 2      /* grouped tcgen05/TMEM GEMM fed by TMA       */
+#define IMX_PATH_GENERIC 3      /* scalar dequant-GEMV, any format            */
+
+/* One quantized tensor: the (weight, scales, biases) triple of a
+ * `QuantizedLinear` (mlx/src/nn/linear.rs:13-20).  biases is NULL for
+ * mxfp8/nvfp4; global_scale is nvfp4's tensor scale (use 1.0 otherwise). */
+typedef struct imx_qtensor {
+    const void* w;
+    const void* scales;
+    const void* biases;
+    float global_scale;
+} imx_qtensor;
+
+/* Parameters of the block: mlx/src/model/config.rs:32-52 (quantization) and
+ * :159-170 (num_experts, num_experts_per_tok, moe_intermediate_size,
+ * shared_expert_intermediate_size, norm_topk_prob). */
+typedef struct imx_moe_config {
+    int hidden;               /* H                                           */
+    int num_experts;          /* E                                           */
+    int top_k;                /* num_experts_per_tok                         */
+    int intermediate;         /* I, expert SwiGLU width                      */
+    int shared_intermediate;  /* Is, 0 = no shared expert                    */
+    int norm_topk_prob;       /* renormalise the k selected probabilities    */
+    int mode;                 /* IMX_MODE_*                                  */
+    int bits;                 /* affine 2/3/4/5/6/8; mxfp8 8; nvfp4 4        */
+    int group_size;           /* affine 32/64/128; mxfp8 32; nvfp4 16        */
+    int path;                 /* IMX_PATH_*                                  */
+} imx_moe_config;
+
+/* Weights of one `MoEMLP` (mlx/src/nn/moe.rs:39-52) in the fused checkpoint
+ * layout that `build_moe_experts` slices (mlx/src/model/qwen35.rs:581-590):
+ * gate_up [E, 2I, .] with the gate rows first, down [E, H, .]. */
+typedef struct imx_moe_weights {
+    const void* router_w;              /* bf16 [E, H]   (moe.rs:41)          */
+    const float* router_logit_bias;    /* fp32 [E] or NULL (synthetic skew)  */
+    imx_qtensor gate_up;               /* [E, 2I, H..]                       */
+    imx_qtensor down;                  /* [E, H, I..]                        */
+    imx_qtensor shared_gate_proj;      /* [Is, H..]     (mlp.rs:12-16)       */
+    imx_qtensor shared_up_proj;        /* [Is, H..]                          */
+    imx_qtensor shared_down_proj;      /* [H, Is..]                          */
+    const void* shared_expert_gate_w;  /* bf16 [1, H]   (moe.rs:47)          */
+} imx_moe_weights;
+
+/* Optional per-stage outputs for parity checks; any pointer may be NULL. */
+typedef struct imx_moe_trace {
+    int32_t* topk_idx;     /* [N, k] expert ids, descending probability      */
+    float* topk_w;         /* [N, k] routing weights                         */
+    int32_t* counts;       /* [E]    assignments per expert                  */
+    int32_t* offsets;      /* [E+1]  exclusive scan of counts                */
+    int32_t* perm;         /* [N*k]  flat assignment index per sorted slot   */
+    int32_t* inv_perm;     /* [N*k]  sorted slot per flat assignment index   */
+    float* shared_gate;    /* [N]    sigmoid(x . w_sg)                       */
+} imx_moe_trace;
+
+/* Message of the last failure on the calling thread ("" if none). */
+IMX_API const char* imx_last_error(void);
+
+/* Library version string. */
+IMX_API const char* imx_version(void);
+
+/* ── the block: MoEMLP::forward_with_stream, mlx/src/nn/moe.rs:55-183 ───── */
+
+/* Scratch bytes imx_moe_forward needs for up to n_tokens tokens. */
+IMX_API int imx_moe_workspace_bytes(const imx_moe_config* cfg, int n_tokens, size_t* bytes);
+
+/* y[N,H] (bf16) = MoE(x[N,H] (bf16)).  Replaces moe.rs:55-183 (router,
+ * softmax, top-k, bucketing, per-expert SwiGLU, weighted combine, gated
+ * shared expert) with no host round trip.  workspace: 256-byte aligned
+ * device memory of at least imx_moe_workspace_bytes(). */
+IMX_API int imx_moe_forward(const imx_moe_config* cfg, const imx_moe_weights* w, const void* x,
+                    int n_tokens, void* y, void* workspace, size_t workspace_bytes,
+                    void* stream, const imx_moe_trace* trace);
+
+/* imx_moe_forward with CUDA events recorded on the stream between its stages;
+ * synchronises and returns the five stage durations in milliseconds:
+ * router, dispatch sort, first expert product (gate/up + SwiGLU), second
+ * expert product (down), combine.  For measurement; not on the serving path. */
+IMX_API int imx_moe_forward_timed(const imx_moe_config* cfg, const imx_moe_weights* w, const void* x,
+                          int n_tokens, void* y, void* workspace, size_t workspace_bytes,
+                          void* stream, float* stage_ms);
+
+/* Same with HOST activations: copies x to the device, runs the block, copies
+ * y back, and synchronises the stream before returning.  The workspace must
+ * be imx_moe_workspace_bytes() + 2*roundup(N*H*2, 256) bytes (the staged x and y). */
+IMX_API int imx_moe_forward_host(const imx_moe_config* cfg, const imx_moe_weights* w,
+                         const void* x_host, int n_tokens, void* y_host, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+/* Reads (and clears) the device status word of a workspace after
+ * synchronising the stream; IMX_ERR_DEVICE if a kernel recorded an error. */
+IMX_API int imx_moe_status(void* workspace, void* stream);
+
+/* ── stages, for expert parallelism and stage-level parity ─────────────── */
+
+/* Router (moe.rs:67-82): logits = x.W_r^T (+bias), fp32 softmax, top-k in
+ * descending order (lower expert id first among equal values), optional
+ * renormalisation; also the shared-expert gate sigmoid(x.w_sg) (moe.rs:174-177)
+ * when w_sg != NULL, and an fp16 copy of x for the expert products. */
+IMX_API int imx_moe_route(const void* x, int n_tokens, int hidden, const void* router_w,
+                  const float* logit_bias, int num_experts, int top_k, int norm_topk_prob,
+                  const void* shared_gate_w, int32_t* topk_idx, float* topk_w,
+                  float* shared_gate, void* x_f16, void* stream);
+
+/* Bucketing (moe.rs:93-104) as a stable counting sort of the n_assign =
+ * N*k expert ids: counts[E], offsets[E+1], perm[n_assign], inv_perm[n_assign].
+ * scratch: imx_moe_sort_scratch_bytes(n_assign, E) bytes. */
+IMX_API int imx_moe_sort_scratch_bytes(int n_assign, int num_experts, size_t* bytes);
+IMX_API int imx_moe_sort(const int32_t* expert_ids, int n_assign, int num_experts, int32_t* counts,
+                 int32_t* offsets, int32_t* perm, int32_t* inv_perm, void* scratch,
+                 size_t scratch_bytes, void* stream);
+
+/* Grouped SwiGLU experts (moe.rs:117-131 with Expert::forward, moe.rs:26-32),
+ * a gather_qmm-style call: for every expert e and every sorted slot
+ * j in [offsets[e], offsets[e+1]):
+ *   out[j, :] = row_scale[j] * down_e( silu(gate_e(a)) * up_e(a) ),
+ *   a = x_f16[row_index[j], :]
+ * x_f16: fp16 [.., H]; out: fp32 [n_rows, H]; row_scale may be NULL (= 1).
+ * gate_up/down hold num_experts stacked matrices.  scratch:
+ * imx_moe_experts_scratch_bytes(). */
+IMX_API int imx_moe_experts_scratch_bytes(const imx_moe_config* cfg, int n_rows, size_t* bytes);
+IMX_API int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const imx_qtensor* down,
+                    int num_experts, const void* x_f16, const int32_t* row_index,
+                    const int32_t* offsets, int n_rows, int max_rows_per_expert,
+                    const float* row_scale, float* out, void* scratch, size_t scratch_bytes,
+                    void* stream);
+
+/* Weighted combine (moe.rs:147-181): y[t] = sum over the k slots of token t,
+ * in ascending sorted-slot order (the order the reference's expert loop
+ * produces them), of rows[inv_perm[t*k+s]] (already weighted) + shared[t]
+ * (already gated; may be NULL), rounded once to bf16. */
+IMX_API int imx_moe_combine(const float* rows, const int32_t* inv_perm, int n_tokens, int top_k,
+                    int hidden, const float* shared_rows, void* y, void* stream);
+
+/* ── the reference's quantized-op surface, mlx/src/ops.rs:630-727 ──────── */
+
+/* out[rows, in] = dequantize(w) (ops.rs:653-686 -> mlx_dequantize).
+ * out_dtype: 0 = bf16, 1 = fp32, 2 = fp16. */
+IMX_API int imx_dequantize(const imx_qtensor* w, int rows, int in, int group_size, int bits, int mode,
+                   int out_dtype, void* out, void* stream);
+
+/* y[m, n_out] = x[m, in] @ dequantize(w[n_out, in])^T when transpose != 0
+ * (ops.rs:695-727 -> mlx_quantized_matmul; every layer on the path calls it
+ * with transpose = true, mlx/src/nn/linear.rs:51-63); with transpose == 0,
+ * y[m, in] = x[m, n_out] @ dequantize(w[n_out, in]).  x, y bf16. */
+IMX_API int imx_quantized_matmul(const void* x, int m, const imx_qtensor* w, int n_out, int in,
+                         int transpose, int group_size, int bits, int mode, void* y,
+                         void* stream);
+
+/* Quantize w[rows, in] (fp32) into packed values, scales and biases
+ * (absent from the reference's wrappers, which only consume checkpoints that
+ * MLX's `quantize` produced; provided to complete the op surface).  For
+ * nvfp4, global_scale is an INPUT (the tensor scale to quantize against). */
+IMX_API int imx_quantize(const float* w, int rows, int in, int group_size, int bits, int mode,
+                 float global_scale, void* w_packed, void* scales, void* biases, void* stream);
+
+/* gather_qmm: y[j, :] = x[lhs_index[j], :] @ dequantize(w[rhs_index[j]])^T for
+ * j < n_rows (bf16 in/out); the per-row form of the grouped expert product
+ * the reference spells as take_axis + quantized_matmul per expert
+ * (moe.rs:124-130). */
+IMX_API int imx_gather_qmm(const void* x, const int32_t* lhs_index, const imx_qtensor* w,
+                   const int32_t* rhs_index, int n_rows, int n_out, int in, int group_size,
+                   int bits, int mode, void* y, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IRONMLX_B200_H */

@@ -1,0 +1,69 @@
+// Combine stage (mlx/src/nn/moe.rs:147-181): per token, the fp32 sum of its k
+// weighted expert rows plus the gated shared-expert row, rounded once to bf16.
+//
+// The reference appends a token's rows while looping over experts in
+// ascending order (moe.rs:117-144) and sums them in that order
+// (moe.rs:154-163); the sorted slot index grows with the expert id, so the
+// kernel sorts the token's k slots and adds in ascending slot order, which
+// also makes the result independent of launch geometry.
+#include "internal.h"
+
+namespace imx {
+
+namespace {
+
+constexpr int kCThreads = 256;
+constexpr int kMaxK = 64;
+
+__global__ void __launch_bounds__(kCThreads)
+combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ inv_perm, int k, int H,
+               const float* __restrict__ shared_rows, __nv_bfloat16* __restrict__ y) {
+    __shared__ int s_slot[kMaxK];
+    const int t = blockIdx.x;
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        for (int s = 0; s < k; ++s) {            // insertion sort, k is tiny
+            int v = inv_perm[(size_t)t * k + s];
+            int j = s;
+            while (j > 0 && s_slot[j - 1] > v) {
+                s_slot[j] = s_slot[j - 1];
+                --j;
+            }
+            s_slot[j] = v;
+        }
+    }
+    __syncthreads();
+    for (int c = tid * 4; c < H; c += kCThreads * 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < k; ++s) {
+            const int slot = s_slot[s];
+            if (slot < 0) continue;              // dropped assignment (moe.rs:100)
+            const float4 v = *reinterpret_cast<const float4*>(rows + (size_t)slot * H + c);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (shared_rows != nullptr) {
+            const float4 v = *reinterpret_cast<const float4*>(shared_rows + (size_t)t * H + c);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(y + (size_t)t * H + c) = o;
+    }
+}
+
+}  // namespace
+
+int launch_combine(const float* rows, const int32_t* inv_perm, int n, int k, int H,
+                   const float* shared_rows, void* y, cudaStream_t stream) {
+    IMX_REQUIRE(k >= 1 && k <= kMaxK, "combine: top_k (%d) must be in 1..%d", k, kMaxK);
+    IMX_REQUIRE(H % 4 == 0, "combine: hidden (%d) must be a multiple of 4", H);
+    if (n == 0) return IMX_OK;
+    combine_kernel<<<n, kCThreads, 0, stream>>>(rows, inv_perm, k, H, shared_rows, (__nv_bfloat16*)y);
+    IMX_CHECK_CUDA(cudaGetLastError());
+    return IMX_OK;
+}
+
+}  // namespace imx

@@ -1,0 +1,112 @@
+// Internal launcher declarations shared by the .cu files of the library.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace imx {
+
+// A slice of one expert's sorted slots handled by one CTA pass of the decode
+// kernels: `rows` consecutive slots starting at `slot0`, all of expert
+// `expert` (== num_experts for the shared expert).
+struct WorkUnit {
+    int32_t expert;
+    int32_t slot0;
+    int32_t rows;
+    int32_t pad;
+};
+
+// Order of the 16 values inside each block of an fp16 activation row.
+struct Order16 {
+    int8_t o[16];
+};
+
+constexpr int kSchedInts = 8;      // work-stealing counters cleared by the sort stage
+constexpr int kUnitRows = 8;       // slots per decode work unit (the n=8 side of the MMA)
+
+struct SortExtras {
+    const float* topk_w = nullptr;
+    int top_k = 1;
+    int32_t* tok_of_slot = nullptr;
+    float* w_of_slot = nullptr;
+    const float* shared_gate = nullptr;
+    int n_tokens = 0;
+    WorkUnit* units = nullptr;
+    int32_t* n_units = nullptr;
+    int unit_rows = kUnitRows;
+    int32_t* sched = nullptr;
+};
+
+int launch_route(const void* x, int n, int H, const void* Wr, const float* logit_bias, int E, int k,
+                 int norm, const void* w_sg, int32_t* topk_idx, float* topk_w, float* shared_gate,
+                 void* x16, const int* order16, cudaStream_t stream);
+
+// Order of the 16 values of each block of an fp16 activation row as the
+// expert kernels of a bit width read them (identity for the generic path).
+void decode_block_order(int bits, int order[16]);
+
+size_t sort_scratch_bytes(int n_assign, int E);
+int launch_sort(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offsets, int32_t* perm,
+                int32_t* inv_perm, void* scratch, size_t scratch_bytes, const SortExtras* ex,
+                cudaStream_t stream);
+
+// Weights of the experts seen by the grouped kernels: `num_experts` stacked
+// matrices plus one optional extra "expert" (id == num_experts) with its own
+// pointers (the shared expert, whose gate and up projections are separate
+// tensors).
+struct ExpertSet {
+    QFormat fmt;
+    int num_experts;
+    // first product: gate rows [0, n_mid) and up rows of the same expert
+    QMat gate, up;                 // expert 0's matrices
+    size_t gu_stride_w, gu_stride_s;   // bytes between consecutive experts
+    QMat down;
+    size_t dn_stride_w, dn_stride_s;
+    int has_extra;
+    QMat x_gate, x_up, x_down;     // the extra expert
+    int n_in;                      // H
+    int n_mid;                     // I   (routed experts)
+    int x_mid;                     // Is  (extra expert)
+};
+
+// act[slot, :] = silu(gate_e(a)) * up_e(a), a = in[row_index[slot]] (fp16), act fp16.
+// out[slot, :] = row_scale[slot] * down_e(act[slot]) (fp32).
+struct GroupedArgs {
+    ExpertSet set;
+    const __half* in;              // fp16 [.., n_in]
+    const int32_t* row_index;      // per slot, row of `in` (nullptr: slot itself)
+    const WorkUnit* units;
+    const int32_t* n_units;
+    int max_units;
+    int32_t* sched;                // [kSchedInts]; decode kernels use [0] and [1]
+    __half* act;                   // fp16 [n_slots, act_stride]
+    int act_stride;
+    const float* row_scale;        // per slot or nullptr
+    float* out;                    // fp32 [n_slots, n_in]
+    int32_t* status;               // device status word
+};
+
+bool decode_mma_supported(const ExpertSet& s);
+// `mid`, when given, is recorded between the first and the second product.
+int launch_decode_mma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
+int launch_generic_grouped(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
+
+int launch_combine(const float* rows, const int32_t* inv_perm, int n, int k, int H,
+                   const float* shared_rows, void* y, cudaStream_t stream);
+
+// Builds the unit list for a caller-given offsets array (stage-level API).
+int launch_build_units(const int32_t* offsets, int E, int unit_rows, WorkUnit* units, int32_t* n_units,
+                       int32_t* sched, cudaStream_t stream);
+
+int launch_dequantize(const QMat& w, int rows, int in, QFormat f, int out_dtype, void* out,
+                      cudaStream_t stream);
+int launch_quantize(const float* w, int rows, int in, QFormat f, float gscale, void* wp, void* scales,
+                    void* biases, cudaStream_t stream);
+int launch_qmm(const void* x, int m, const QMat& w, int n_out, int in, int transpose, QFormat f, void* y,
+               const int32_t* lhs_index, const int32_t* rhs_index, size_t w_stride, size_t s_stride,
+               cudaStream_t stream);
+
+int validate_format(int mode, int bits, int group, QFormat* out);
+
+}  // namespace imx

@@ -1,0 +1,218 @@
+// Router stage of the MoE block (mlx/src/nn/moe.rs:67-82 and :174-177):
+//   logits = x . W_r^T  (bf16 inputs, fp32 accumulation)
+//   probs  = softmax(logits) in fp32
+//   top-k of probs in descending order, lower expert id first among equals
+//   weights = probs[top] (/ their sum when norm_topk_prob)
+//   shared gate = sigmoid(x . w_sg)
+// plus an fp16 copy of x, the operand type of the expert products.
+//
+// One thread-block CLUSTER per token: the experts are split across the
+// cluster's CTAs (so a 64-token decode batch still fills the GPU), partial
+// logit vectors are written into the leader CTA's shared memory through
+// distributed shared memory, and one warp of the leader does softmax/top-k
+// with shuffle reductions.  HBM traffic is W_r once (L2-resident afterwards)
+// plus x; the stage is latency-bound, not bandwidth-bound.
+#include <cooperative_groups.h>
+
+#include "internal.h"
+
+namespace cg = cooperative_groups;
+
+namespace imx {
+
+namespace {
+
+constexpr int kRouteThreads = 256;
+
+
+template <int JMAX>
+__device__ void softmax_topk_warp(const float* s_logits, int E, int k, bool norm, int32_t* out_idx,
+                                  float* out_w) {
+    const int lane = threadIdx.x & 31;
+    float p[JMAX];
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < JMAX; ++j) {
+        int e = lane + 32 * j;
+        p[j] = e < E ? s_logits[e] : -INFINITY;
+        m = fmaxf(m, p[j]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < JMAX; ++j) {
+        int e = lane + 32 * j;
+        p[j] = e < E ? expf(p[j] - m) : 0.f;
+        s += p[j];
+    }
+    s = warp_sum(s);
+#pragma unroll
+    for (int j = 0; j < JMAX; ++j) {
+        int e = lane + 32 * j;
+        p[j] = e < E ? p[j] / s : -1.f;   // -1 marks "not selectable"
+    }
+    float my_w = 0.f;
+    int my_i = 0;
+    float wsum = 0.f;
+    for (int r = 0; r < k; ++r) {
+        float bv = -1.f;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < JMAX; ++j) {
+            if (p[j] > bv) {           // ascending j: lower id wins ties inside a lane
+                bv = p[j];
+                bi = lane + 32 * j;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < JMAX; ++j)
+            if (lane + 32 * j == bi) p[j] = -1.f;
+        if (lane == (r & 31)) {
+            my_w = bv;
+            my_i = bi;
+        }
+        wsum += bv;
+        if ((r & 31) == 31 || r == k - 1) {      // flush up to 32 results
+            int slot = (r & ~31) + lane;
+            if (slot <= r) {
+                out_idx[slot] = my_i;
+                out_w[slot] = my_w;               // normalised below
+            }
+        }
+    }
+    __syncwarp();
+    if (norm) {
+        for (int slot = lane; slot < k; slot += 32) out_w[slot] = out_w[slot] / wsum;
+    }
+}
+
+__global__ void __launch_bounds__(kRouteThreads)
+route_kernel(const __nv_bfloat16* __restrict__ x, int H, const __nv_bfloat16* __restrict__ Wr,
+             const float* __restrict__ logit_bias, int E, int k, int norm,
+             const __nv_bfloat16* __restrict__ w_sg, int32_t* __restrict__ topk_idx,
+             float* __restrict__ topk_w, float* __restrict__ shared_gate,
+             __half* __restrict__ x16, const Order16 order) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* s_x = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    float* s_logits = reinterpret_cast<float*>(smem_raw + (size_t)H * 2);
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int cs = (int)cluster.num_blocks();
+    const int rank = (int)cluster.block_rank();
+    const int token = blockIdx.x / cs;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int nwarps = kRouteThreads / 32;
+
+    const __nv_bfloat16* xr = x + (size_t)token * H;
+    for (int c = tid * 8; c < H; c += kRouteThreads * 8) {
+        uint4 v = *reinterpret_cast<const uint4*>(xr + c);
+        *reinterpret_cast<uint4*>(s_x + c) = v;
+    }
+    __syncthreads();
+    if (rank == 0 && x16 != nullptr) {
+        // fp16 copy; inside every block of 16 the values are stored in the
+        // order the expert kernels consume them (identity for the generic path)
+        __half2* dst = reinterpret_cast<__half2*>(x16 + (size_t)token * H);
+        for (int i = tid; i < H / 2; i += kRouteThreads) {
+            const int blk = (2 * i) & ~15, p = (2 * i) & 15;
+            const float a = __bfloat162float(s_x[blk + order.o[p]]);
+            const float b = __bfloat162float(s_x[blk + order.o[p + 1]]);
+            dst[i] = __halves2half2(f32_to_f16_sat(a), f32_to_f16_sat(b));
+        }
+    }
+
+    float* leader_logits = cluster.map_shared_rank(s_logits, 0);
+    const int per = (E + cs - 1) / cs;
+    const int e_lo = rank * per;
+    const int e_hi = min(E, e_lo + per);
+    // the last CTA of the cluster also owns the shared-gate dot product (index E)
+    const int n_rows = (e_hi - e_lo) + ((rank == cs - 1 && w_sg != nullptr) ? 1 : 0);
+    for (int r = warp; r < n_rows; r += nwarps) {
+        const bool is_gate = (e_lo + r >= e_hi);
+        const __nv_bfloat16* wrow = is_gate ? w_sg : Wr + (size_t)(e_lo + r) * H;
+        float acc = 0.f;
+        for (int c = lane * 8; c < H; c += 256) {
+            uint4 wv = *reinterpret_cast<const uint4*>(wrow + c);
+            uint4 xv = *reinterpret_cast<const uint4*>(s_x + c);
+            const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+            const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float2 wf = __bfloat1622float2(wb[i]);
+                float2 xf = __bfloat1622float2(xb[i]);
+                acc = fmaf(wf.x, xf.x, acc);
+                acc = fmaf(wf.y, xf.y, acc);
+            }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            if (is_gate) {
+                shared_gate[token] = 1.0f / (1.0f + expf(-acc));
+            } else {
+                if (logit_bias != nullptr) acc += logit_bias[e_lo + r];
+                leader_logits[e_lo + r] = acc;
+            }
+        }
+    }
+    cluster.sync();
+    if (rank == 0 && warp == 0) {
+        int32_t* oi = topk_idx + (size_t)token * k;
+        float* ow = topk_w + (size_t)token * k;
+        const int j = (E + 31) / 32;
+        if (j <= 1) softmax_topk_warp<1>(s_logits, E, k, norm, oi, ow);
+        else if (j <= 2) softmax_topk_warp<2>(s_logits, E, k, norm, oi, ow);
+        else if (j <= 4) softmax_topk_warp<4>(s_logits, E, k, norm, oi, ow);
+        else if (j <= 8) softmax_topk_warp<8>(s_logits, E, k, norm, oi, ow);
+        else if (j <= 16) softmax_topk_warp<16>(s_logits, E, k, norm, oi, ow);
+        else softmax_topk_warp<32>(s_logits, E, k, norm, oi, ow);
+    }
+}
+
+}  // namespace
+
+int launch_route(const void* x, int n, int H, const void* Wr, const float* logit_bias, int E, int k,
+                 int norm, const void* w_sg, int32_t* topk_idx, float* topk_w, float* shared_gate,
+                 void* x16, const int* order16, cudaStream_t stream) {
+    IMX_REQUIRE(n >= 0 && H > 0 && H % 16 == 0, "route: hidden (%d) must be a positive multiple of 16", H);
+    Order16 order;
+    for (int i = 0; i < 16; ++i) order.o[i] = (int8_t)(order16 ? order16[i] : i);
+    IMX_REQUIRE(E >= 1 && E <= 1024, "route: num_experts (%d) must be in 1..1024", E);
+    IMX_REQUIRE(k >= 1 && k <= E, "route: top_k (%d) must be in 1..num_experts (%d)", k, E);
+    IMX_REQUIRE(w_sg == nullptr || shared_gate != nullptr, "route: shared gate weight without output");
+    if (n == 0) return IMX_OK;
+    // cluster size: enough CTAs to cover the GPU at small N, experts split evenly
+    int cs = 1;
+    while (cs < 8 && (long)n * cs < 296 && E / (cs * 2) >= 16) cs *= 2;
+    size_t smem = (size_t)H * 2 + (size_t)E * 4;
+    IMX_REQUIRE(smem <= 200 * 1024, "route: hidden %d / experts %d exceed shared memory", H, E);
+    IMX_CHECK_CUDA(cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)(n * cs));
+    lc.blockDim = dim3(kRouteThreads);
+    lc.dynamicSmemBytes = smem;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    IMX_CHECK_CUDA(cudaLaunchKernelEx(&lc, route_kernel, (const __nv_bfloat16*)x, H,
+                                      (const __nv_bfloat16*)Wr, logit_bias, E, k, norm,
+                                      (const __nv_bfloat16*)w_sg, topk_idx, topk_w, shared_gate,
+                                      (__half*)x16, order));
+    return IMX_OK;
+}
+
+}  // namespace imx

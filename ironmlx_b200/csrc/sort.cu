@@ -1,0 +1,337 @@
+// Dispatch stage of the MoE block: the host bucketing loop of
+// mlx/src/nn/moe.rs:93-104 as a deterministic, stable counting sort on the GPU.
+//
+// The reference walks tokens in order and slots in order and appends
+// (token, token*k+slot) to its expert's list, so the dispatch permutation is
+// the STABLE sort of the flat assignment indices by expert id.  Here:
+//   rank  each warp ranks 32 ids at a time with __match_any_sync (peers with
+//         the same expert, lower lanes first) on top of a per-warp running
+//         histogram in shared memory; no order-dependent atomics anywhere
+//   scan  per expert, an exclusive scan over warps (and over blocks when the
+//         input spans several), then an exclusive scan over experts
+//   place perm[offset[e] + block base + warp base + rank] = flat index
+// Small inputs (decode) run the three steps in ONE single-block kernel that
+// also emits the per-slot gather/scale arrays and the work-unit list of the
+// expert kernels; large inputs use three launches.
+#include "common.cuh"
+#include "internal.h"
+
+namespace imx {
+
+namespace {
+
+constexpr int kSortThreads = 1024;
+constexpr int kSortWarps = kSortThreads / 32;
+constexpr int kSortChunk = 4096;   // ids per block in the multi-block path
+
+// Block-wide exclusive scan of one int per thread (all threads must call).
+__device__ int block_exclusive_scan(int v, int* s_warp /*[32]*/, int* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = (lane < (int)(blockDim.x >> 5)) ? s_warp[lane] : 0;
+        int winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int t = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += t;
+        }
+        s_warp[lane] = winc - w;   // exclusive warp base
+        if (lane == 31) s_warp[32] = winc;
+    }
+    __syncthreads();
+    int res = s_warp[warp] + inc - v;
+    if (total) *total = s_warp[32];
+    __syncthreads();
+    return res;
+}
+
+// Step 1 for the ids [lo, hi) of this block: block-local stable rank of every
+// id among equal ids (written to rank_out) and per-expert totals left in
+// s_hist[0][e]..: on return s_tot[e] holds the block's count of expert e.
+__device__ void block_rank(const int32_t* __restrict__ ids, int lo, int hi, int E,
+                           int* s_hist /*[kSortWarps][E]*/, int* s_tot /*[E]*/,
+                           int32_t* __restrict__ rank_out) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < kSortWarps * E; i += kSortThreads) s_hist[i] = 0;
+    __syncthreads();
+    const int n = hi - lo;
+    int per_warp = ((n + kSortWarps - 1) / kSortWarps + 31) & ~31;
+    const int w_lo = lo + warp * per_warp;
+    const int w_hi = min(hi, w_lo + per_warp);
+    int* my_hist = s_hist + warp * E;
+    const unsigned lt = (1u << lane) - 1u;
+    for (int base = w_lo; base < w_hi; base += 32) {
+        const int i = base + lane;
+        int e = (i < w_hi) ? ids[i] : -1;
+        if (e < 0 || e >= E) e = -1;                    // moe.rs:100: out-of-range ids are dropped
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        int before = 0;
+        if (e >= 0) before = my_hist[e];
+        __syncwarp();
+        if (e >= 0) {
+            const int r = __popc(peers & lt);
+            if (r == 0) my_hist[e] = before + __popc(peers);
+            rank_out[i] = before + r;
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    // exclusive scan over warps, per expert
+    for (int e = tid; e < E; e += kSortThreads) {
+        int run = 0;
+        for (int w = 0; w < kSortWarps; ++w) {
+            int t = s_hist[w * E + e];
+            s_hist[w * E + e] = run;
+            run += t;
+        }
+        s_tot[e] = run;
+    }
+    __syncthreads();
+    // fold the warp base into the stored ranks
+    for (int base = w_lo; base < w_hi; base += 32) {
+        const int i = base + lane;
+        if (i < w_hi) {
+            int e = ids[i];
+            if (e >= 0 && e < E) rank_out[i] += my_hist[e];
+        }
+    }
+}
+
+// Exclusive scan of s_tot[0..E) into offsets[0..E] (E <= 1024 = blockDim).
+__device__ void scan_experts(const int* s_tot, int E, int32_t* __restrict__ offsets, int* s_off,
+                             int* s_warp) {
+    const int tid = threadIdx.x;
+    int v = tid < E ? s_tot[tid] : 0;
+    int total;
+    int ex = block_exclusive_scan(v, s_warp, &total);
+    if (tid < E) {
+        s_off[tid] = ex;
+        offsets[tid] = ex;
+    }
+    if (tid == 0) {
+        s_off[E] = total;
+        offsets[E] = total;
+    }
+    __syncthreads();
+}
+
+struct SortAux {
+    // optional extras emitted by the fused kernel (all may be null)
+    const float* topk_w;     // [A] routing weight per flat assignment
+    int top_k;
+    int32_t* tok_of_slot;    // [A (+N)] token id per sorted slot
+    float* w_of_slot;        // [A (+N)] routing weight per sorted slot
+    const float* shared_gate;// [N] or null: appended after the A routed slots
+    int n_tokens;
+    WorkUnit* units;         // work units of `unit_rows` rows
+    int32_t* n_units;
+    int unit_rows;
+    int32_t* sched;          // scheduler counters to clear (kSchedInts ints)
+};
+
+__device__ void emit_aux(const SortAux& aux, const int32_t* __restrict__ perm, const int* s_off,
+                         int E, int A, int* s_warp) {
+    const int tid = threadIdx.x;
+    if (aux.sched != nullptr && tid < kSchedInts) aux.sched[tid] = 0;
+    if (aux.tok_of_slot != nullptr) {
+        const int total = s_off[E];
+        for (int j = tid; j < total; j += kSortThreads) {
+            int f = perm[j];
+            aux.tok_of_slot[j] = f / aux.top_k;
+            if (aux.w_of_slot) aux.w_of_slot[j] = aux.topk_w ? aux.topk_w[f] : 1.f;
+        }
+        if (aux.shared_gate != nullptr) {
+            for (int t = tid; t < aux.n_tokens; t += kSortThreads) {
+                aux.tok_of_slot[A + t] = t;
+                if (aux.w_of_slot) aux.w_of_slot[A + t] = aux.shared_gate[t];
+            }
+        }
+    }
+    if (aux.units != nullptr) {
+        const int ur = aux.unit_rows;
+        // E routed experts + (optionally) the shared expert as pseudo-expert E
+        const bool has_shared = aux.shared_gate != nullptr;
+        int cnt = 0, pos0 = 0;
+        if (tid < E) {
+            cnt = s_off[tid + 1] - s_off[tid];
+            pos0 = s_off[tid];
+        } else if (tid == E && has_shared) {
+            cnt = aux.n_tokens;
+            pos0 = A;
+        }
+        int nu = (cnt + ur - 1) / ur;
+        int total;
+        int base = block_exclusive_scan(nu, s_warp, &total);
+        for (int c = 0; c < nu; ++c) {
+            WorkUnit u;
+            u.expert = tid;
+            u.slot0 = pos0 + c * ur;
+            u.rows = min(ur, cnt - c * ur);
+            u.pad = 0;
+            aux.units[base + c] = u;
+        }
+        if (tid == 0) *aux.n_units = total;
+    }
+}
+
+// One block does everything (A <= kSortChunk).
+__global__ void __launch_bounds__(kSortThreads)
+sort_fused_kernel(const int32_t* __restrict__ ids, int A, int E, int32_t* __restrict__ counts,
+                  int32_t* __restrict__ offsets, int32_t* __restrict__ perm,
+                  int32_t* __restrict__ inv_perm, SortAux aux) {
+    extern __shared__ int s_mem[];
+    int* s_hist = s_mem;                       // [kSortWarps][E]
+    int* s_tot = s_hist + kSortWarps * E;      // [E]
+    int* s_off = s_tot + E;                    // [E+1]
+    int* s_warp = s_off + E + 1;               // [33]
+    block_rank(ids, 0, A, E, s_hist, s_tot, inv_perm);
+    __syncthreads();
+    const int tid = threadIdx.x;
+    if (tid < E && counts != nullptr) counts[tid] = s_tot[tid];
+    scan_experts(s_tot, E, offsets, s_off, s_warp);
+    for (int i = tid; i < A; i += kSortThreads) {
+        int e = ids[i];
+        if (e >= 0 && e < E) {
+            int pos = s_off[e] + inv_perm[i];
+            perm[pos] = i;
+            inv_perm[i] = pos;
+        } else {
+            inv_perm[i] = -1;
+        }
+    }
+    __syncthreads();
+    emit_aux(aux, perm, s_off, E, A, s_warp);
+}
+
+// Multi-block path, launch 1: ranks inside each block + per-block totals.
+__global__ void __launch_bounds__(kSortThreads)
+sort_rank_kernel(const int32_t* __restrict__ ids, int A, int E, int32_t* __restrict__ rank_tmp,
+                 int32_t* __restrict__ block_counts /*[nb][E]*/) {
+    extern __shared__ int s_mem[];
+    int* s_hist = s_mem;
+    int* s_tot = s_hist + kSortWarps * E;
+    const int lo = blockIdx.x * kSortChunk;
+    const int hi = min(A, lo + kSortChunk);
+    block_rank(ids, lo, hi, E, s_hist, s_tot, rank_tmp);
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += kSortThreads) block_counts[(size_t)blockIdx.x * E + e] = s_tot[e];
+}
+
+// Launch 2 (one block): scan over blocks per expert, then over experts.
+__global__ void __launch_bounds__(kSortThreads)
+sort_scan_kernel(int32_t* __restrict__ block_counts, int nb, int E, int32_t* __restrict__ counts,
+                 int32_t* __restrict__ offsets, SortAux aux, int A) {
+    extern __shared__ int s_mem[];
+    int* s_tot = s_mem;             // [E]
+    int* s_off = s_tot + E;         // [E+1]
+    int* s_warp = s_off + E + 1;    // [33]
+    const int tid = threadIdx.x;
+    if (tid < E) {
+        int run = 0;
+        for (int b = 0; b < nb; ++b) {
+            int t = block_counts[(size_t)b * E + tid];
+            block_counts[(size_t)b * E + tid] = run;
+            run += t;
+        }
+        s_tot[tid] = run;
+        if (counts != nullptr) counts[tid] = run;
+    }
+    __syncthreads();
+    scan_experts(s_tot, E, offsets, s_off, s_warp);
+    // unit list and scheduler reset only (the per-slot arrays need perm: launch 3)
+    SortAux a2 = aux;
+    a2.tok_of_slot = nullptr;
+    emit_aux(a2, nullptr, s_off, E, A, s_warp);
+}
+
+// Launch 3: place.
+__global__ void __launch_bounds__(256)
+sort_place_kernel(const int32_t* __restrict__ ids, int A, int E, const int32_t* __restrict__ offsets,
+                  const int32_t* __restrict__ block_counts, int32_t* __restrict__ perm,
+                  int32_t* __restrict__ inv_perm /* holds ranks on entry */, SortAux aux) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < A) {
+        int e = ids[i];
+        if (e >= 0 && e < E) {
+            int b = i / kSortChunk;
+            int pos = offsets[e] + block_counts[(size_t)b * E + e] + inv_perm[i];
+            perm[pos] = i;
+            inv_perm[i] = pos;
+            if (aux.tok_of_slot != nullptr) {
+                aux.tok_of_slot[pos] = i / aux.top_k;
+                if (aux.w_of_slot) aux.w_of_slot[pos] = aux.topk_w ? aux.topk_w[i] : 1.f;
+            }
+        } else {
+            inv_perm[i] = -1;
+        }
+    }
+    if (aux.tok_of_slot != nullptr && aux.shared_gate != nullptr && i < aux.n_tokens) {
+        aux.tok_of_slot[A + i] = i;
+        if (aux.w_of_slot) aux.w_of_slot[A + i] = aux.shared_gate[i];
+    }
+}
+
+}  // namespace
+
+size_t sort_scratch_bytes(int n_assign, int E) {
+    int nb = ceil_div(n_assign > 0 ? n_assign : 1, kSortChunk);
+    return align_up((size_t)nb * E * sizeof(int32_t), 256);
+}
+
+int launch_sort(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offsets, int32_t* perm,
+                int32_t* inv_perm, void* scratch, size_t scratch_bytes, const SortExtras* ex,
+                cudaStream_t stream) {
+    IMX_REQUIRE(A >= 0 && E >= 1 && E <= 1024, "sort: num_experts (%d) must be in 1..1024", E);
+    IMX_REQUIRE(offsets && perm && inv_perm, "sort: offsets, perm and inv_perm are required");
+    SortAux aux = {};
+    if (ex != nullptr) {
+        aux.topk_w = ex->topk_w;
+        aux.top_k = ex->top_k > 0 ? ex->top_k : 1;
+        aux.tok_of_slot = ex->tok_of_slot;
+        aux.w_of_slot = ex->w_of_slot;
+        aux.shared_gate = ex->shared_gate;
+        aux.n_tokens = ex->n_tokens;
+        aux.units = ex->units;
+        aux.n_units = ex->n_units;
+        aux.unit_rows = ex->unit_rows > 0 ? ex->unit_rows : 8;
+        aux.sched = ex->sched;
+        IMX_REQUIRE(aux.units == nullptr || E + 1 <= kSortThreads, "sort: too many experts for the unit list");
+    }
+    const size_t smem_fused = ((size_t)kSortWarps * E + E + E + 1 + 33) * sizeof(int);
+    if (A <= kSortChunk) {
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(sort_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)smem_fused));
+        sort_fused_kernel<<<1, kSortThreads, smem_fused, stream>>>(ids, A, E, counts, offsets, perm,
+                                                                   inv_perm, aux);
+        IMX_CHECK_CUDA(cudaGetLastError());
+        return IMX_OK;
+    }
+    const int nb = ceil_div(A, kSortChunk);
+    IMX_REQUIRE(scratch != nullptr && scratch_bytes >= (size_t)nb * E * sizeof(int32_t),
+                "sort: scratch of %zu bytes needed, %zu given", (size_t)nb * E * sizeof(int32_t), scratch_bytes);
+    int32_t* block_counts = (int32_t*)scratch;
+    const size_t smem_rank = ((size_t)kSortWarps * E + E) * sizeof(int);
+    IMX_CHECK_CUDA(cudaFuncSetAttribute(sort_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem_rank));
+    sort_rank_kernel<<<nb, kSortThreads, smem_rank, stream>>>(ids, A, E, inv_perm, block_counts);
+    IMX_CHECK_CUDA(cudaGetLastError());
+    const size_t smem_scan = ((size_t)E + E + 1 + 33) * sizeof(int);
+    sort_scan_kernel<<<1, kSortThreads, smem_scan, stream>>>(block_counts, nb, E, counts, offsets, aux, A);
+    IMX_CHECK_CUDA(cudaGetLastError());
+    int place_n = A;
+    if (aux.tok_of_slot && aux.shared_gate && aux.n_tokens > place_n) place_n = aux.n_tokens;
+    sort_place_kernel<<<ceil_div(place_n, 256), 256, 0, stream>>>(ids, A, E, offsets, block_counts, perm,
+                                                                 inv_perm, aux);
+    IMX_CHECK_CUDA(cudaGetLastError());
+    return IMX_OK;
+}
+
+}  // namespace imx

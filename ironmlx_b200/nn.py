@@ -1,0 +1,272 @@
+"""Host-side mirror of the layer types on the MoE path of the reference:
+`Linear`, `QuantizedLinear`, `LinearLayer` (mlx/src/nn/linear.rs), `MLP`
+(mlx/src/nn/mlp.rs), `Expert` and `MoEMLP` (mlx/src/nn/moe.rs:11-52), with
+the same field names and `forward_with_stream(x, stream)` entry points, so
+model code that builds these structs literally
+(mlx/src/model/qwen35.rs:489-531) keeps working.
+
+`MoEMLP.forward_with_stream` is one call into the C ABI (`imx_moe_forward`);
+the per-expert host loop, the mid-layer device->host sync and the per-row
+graph nodes of the reference (moe.rs:86-170) do not exist here.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from . import _lib
+from . import ops
+from ._lib import IronMLXError, MoEConfig, MoETrace, MoEWeights, QTensor, check, lib
+
+
+@dataclass
+class Linear:
+    """Dense `x @ W^T (+ b)` (mlx/src/nn/linear.rs:129-177).  On the MoE path
+    only the router and the shared-expert gate are dense, and both are consumed
+    inside the fused block, so this class only carries the weights."""
+    weight: torch.Tensor
+    bias: Optional[torch.Tensor] = None
+
+    def forward_with_stream(self, x: torch.Tensor, stream=None) -> torch.Tensor:
+        raise IronMLXError(_lib.ERR_INVALID,
+                           "dense Linear is not part of the accelerated path; it is evaluated inside MoEMLP")
+
+
+@dataclass
+class QuantizedLinear:
+    """mlx/src/nn/linear.rs:13-63: packed weight + per-group scales/biases,
+    forward = `quantized_matmul(x, w, scales, biases, transpose=true, ...)`."""
+    weight: torch.Tensor
+    scales: torch.Tensor
+    biases: Optional[torch.Tensor]
+    group_size: int = 64
+    bits: int = 4
+    mode: str = "affine"
+    global_scale: Optional[float] = None
+
+    @classmethod
+    def new(cls, weight, scales, biases, group_size: int, bits: int) -> "QuantizedLinear":
+        return cls(weight, scales, biases, group_size, bits, "affine")
+
+    @classmethod
+    def new_with_mode(cls, weight, scales, biases, group_size: int, bits: int, mode: str,
+                      global_scale: Optional[float] = None) -> "QuantizedLinear":
+        return cls(weight, scales, biases, group_size, bits, mode, global_scale)
+
+    def forward_with_stream(self, x: torch.Tensor, stream=None) -> torch.Tensor:
+        return ops.quantized_matmul(x, self.weight, self.scales, self.biases, True, self.group_size,
+                                    self.bits, self.mode, stream, self.global_scale)
+
+    def qtensor(self) -> QTensor:
+        return ops.qtensor(self.weight, self.scales, self.biases, self.global_scale)
+
+
+LinearLayer = Union[Linear, QuantizedLinear]
+
+
+@dataclass
+class MLP:
+    """SwiGLU MLP, `down(silu(gate(x)) * up(x))` (mlx/src/nn/mlp.rs:12-33);
+    the shared expert of the block."""
+    gate_proj: QuantizedLinear
+    up_proj: QuantizedLinear
+    down_proj: QuantizedLinear
+
+
+@dataclass
+class Expert:
+    """One routed expert (mlx/src/nn/moe.rs:11-33).  Its three projections are
+    views into the fused [E, 2I, .] / [E, H, .] checkpoint tensors
+    (mlx/src/model/qwen35.rs:661-776)."""
+    gate_proj: QuantizedLinear
+    up_proj: QuantizedLinear
+    down_proj: QuantizedLinear
+
+
+def _stack_or_view(parts: Sequence[torch.Tensor]) -> torch.Tensor:
+    """[E] equally shaped tensors -> one contiguous [E, ...] tensor; no copy
+    when they already are consecutive slices of one allocation."""
+    first = parts[0]
+    step = first.numel() * first.element_size()
+    if all(p.is_contiguous() and p.data_ptr() == first.data_ptr() + i * step for i, p in enumerate(parts)):
+        base = first.as_strided((len(parts),) + tuple(first.shape), (first.numel(),) + tuple(first.stride()))
+        return base
+    return torch.stack([p.contiguous() for p in parts])
+
+
+class MoEMLP:
+    """Mixture-of-experts MLP with a gated shared expert (mlx/src/nn/moe.rs:39-52).
+
+    Fields keep the reference's names: gate (router), experts, shared_expert,
+    shared_expert_gate, num_experts_per_tok, norm_topk_prob.
+    """
+
+    def __init__(self, gate: Linear, experts: Union[List[Expert], "FusedExperts"],
+                 shared_expert: Optional[MLP], shared_expert_gate: Optional[Linear],
+                 num_experts_per_tok: int, norm_topk_prob: bool = True,
+                 router_logit_bias: Optional[torch.Tensor] = None, path: str = "auto"):
+        self.gate = gate
+        self.experts = experts
+        self.shared_expert = shared_expert
+        self.shared_expert_gate = shared_expert_gate
+        self.num_experts_per_tok = int(num_experts_per_tok)
+        self.norm_topk_prob = bool(norm_topk_prob)
+        self.router_logit_bias = router_logit_bias
+        self.path = path
+        self._fused = experts if isinstance(experts, FusedExperts) else FusedExperts.from_experts(experts)
+        self._workspace = None
+        f = self._fused
+        self.num_experts = f.gate_up.weight.shape[0]
+        self.hidden = gate.weight.shape[1]
+        self.intermediate = f.gate_up.weight.shape[1] // 2
+        self.shared_intermediate = 0 if shared_expert is None else shared_expert.gate_proj.weight.shape[0]
+        if gate.weight.shape[0] != self.num_experts:
+            raise IronMLXError(_lib.ERR_INVALID, "router rows must equal the number of experts")
+        if (shared_expert is None) != (shared_expert_gate is None):
+            raise IronMLXError(_lib.ERR_INVALID, "shared_expert and shared_expert_gate go together")
+
+    # -- C structs ----------------------------------------------------------
+    def config(self, path: Optional[str] = None) -> MoEConfig:
+        q = self._fused.gate_up
+        return MoEConfig(self.hidden, self.num_experts, self.num_experts_per_tok, self.intermediate,
+                         self.shared_intermediate, int(self.norm_topk_prob), _lib.MODE[q.mode], q.bits,
+                         q.group_size, _lib.PATH[path or self.path])
+
+    def weights(self) -> MoEWeights:
+        w = MoEWeights()
+        w.router_w = self.gate.weight.data_ptr()
+        w.router_logit_bias = None if self.router_logit_bias is None else self.router_logit_bias.data_ptr()
+        w.gate_up = self._fused.gate_up.qtensor()
+        w.down = self._fused.down.qtensor()
+        if self.shared_expert is not None:
+            w.shared_gate_proj = self.shared_expert.gate_proj.qtensor()
+            w.shared_up_proj = self.shared_expert.up_proj.qtensor()
+            w.shared_down_proj = self.shared_expert.down_proj.qtensor()
+            w.shared_expert_gate_w = self.shared_expert_gate.weight.data_ptr()
+        return w
+
+    def workspace_bytes(self, n_tokens: int, host_io: bool = False) -> int:
+        cfg = self.config()
+        out = C.c_size_t(0)
+        check(lib().imx_moe_workspace_bytes(C.byref(cfg), n_tokens, C.byref(out)))
+        extra = 2 * ((n_tokens * self.hidden * 2 + 255) // 256 * 256) if host_io else 0
+        return out.value + extra
+
+    def _ws(self, n_tokens: int, device, host_io: bool = False) -> torch.Tensor:
+        need = self.workspace_bytes(n_tokens, host_io)
+        if self._workspace is None or self._workspace.numel() < need or self._workspace.device != device:
+            self._workspace = torch.zeros(need, dtype=torch.uint8, device=device)
+        return self._workspace
+
+    # -- forward ------------------------------------------------------------
+    def forward_with_stream(self, x: torch.Tensor, stream=None, trace: bool = False, path: Optional[str] = None):
+        """x: bf16 [B, L, H] (or [N, H]) -> same shape (moe.rs:55-183).
+        With trace=True also returns the per-stage tensors as a dict."""
+        if x.dtype != torch.bfloat16 or not x.is_cuda:
+            raise IronMLXError(_lib.ERR_INVALID, "MoEMLP: x must be a bfloat16 CUDA tensor")
+        if x.shape[-1] != self.hidden:
+            raise IronMLXError(_lib.ERR_INVALID, f"MoEMLP: last dimension {x.shape[-1]} != hidden {self.hidden}")
+        x = x.contiguous()
+        n = x.numel() // self.hidden
+        y = torch.empty_like(x)
+        ws = self._ws(n, x.device)
+        cfg, w = self.config(path), self.weights()
+        tr, tensors = None, None
+        if trace:
+            k, e = self.num_experts_per_tok, self.num_experts
+            i32 = dict(dtype=torch.int32, device=x.device)
+            tensors = {
+                "topk_idx": torch.empty(n, k, **i32), "topk_w": torch.empty(n, k, device=x.device),
+                "counts": torch.empty(e, **i32), "offsets": torch.empty(e + 1, **i32),
+                "perm": torch.empty(n * k, **i32), "inv_perm": torch.empty(n * k, **i32),
+                "shared_gate": torch.empty(n, device=x.device),
+            }
+            tr = MoETrace(**{name: t.data_ptr() for name, t in tensors.items()})
+        check(lib().imx_moe_forward(C.byref(cfg), C.byref(w), x.data_ptr(), n, y.data_ptr(), ws.data_ptr(),
+                                    ws.numel(), ops.stream_ptr(stream), None if tr is None else C.byref(tr)))
+        return (y, tensors) if trace else y
+
+    def forward_timed(self, x: torch.Tensor, stream=None):
+        """-> (y, [router, sort, gate/up, down, combine] milliseconds), measured
+        with CUDA events recorded between the stages on the stream."""
+        x = x.contiguous()
+        n = x.numel() // self.hidden
+        y = torch.empty_like(x)
+        ws = self._ws(n, x.device)
+        cfg, w = self.config(), self.weights()
+        ms = (C.c_float * 5)()
+        check(lib().imx_moe_forward_timed(C.byref(cfg), C.byref(w), x.data_ptr(), n, y.data_ptr(), ws.data_ptr(),
+                                          ws.numel(), ops.stream_ptr(stream), ms))
+        return y, list(ms)
+
+    def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor, stream=None) -> torch.Tensor:
+        """Host-resident bf16 activations in and out (pinned memory recommended):
+        H2D copy, the block, D2H copy and a stream sync inside one ABI call."""
+        n = x_host.numel() // self.hidden
+        dev = self.gate.weight.device
+        ws = self._ws(n, dev, host_io=True)
+        cfg, w = self.config(), self.weights()
+        check(lib().imx_moe_forward_host(C.byref(cfg), C.byref(w), x_host.data_ptr(), n, y_host.data_ptr(),
+                                         ws.data_ptr(), ws.numel(), ops.stream_ptr(stream)))
+        return y_host
+
+    def check_status(self, stream=None) -> None:
+        if self._workspace is not None:
+            check(lib().imx_moe_status(self._workspace.data_ptr(), ops.stream_ptr(stream)))
+
+
+@dataclass
+class FusedExperts:
+    """All routed experts as the two fused checkpoint tensors:
+    gate_up [E, 2I, .] (gate rows first) and down [E, H, .]
+    (mlx/src/model/qwen35.rs:581-590)."""
+    gate_up: QuantizedLinear
+    down: QuantizedLinear
+
+    @classmethod
+    def from_experts(cls, experts: Sequence[Expert]) -> "FusedExperts":
+        if len(experts) == 0:
+            raise IronMLXError(_lib.ERR_INVALID, "MoEMLP needs at least one expert")
+        e0 = experts[0]
+        q = e0.gate_proj
+
+        def fuse(get):
+            parts = [get(e) for e in experts]
+            return _stack_or_view(parts)
+
+        def gu(attr):
+            # per expert, gate rows then up rows; a view when they are adjacent slices
+            rows = []
+            for e in experts:
+                g, u = getattr(e.gate_proj, attr), getattr(e.up_proj, attr)
+                if g is None:
+                    return None
+                step = g.numel() * g.element_size()
+                if g.is_contiguous() and u.is_contiguous() and u.data_ptr() == g.data_ptr() + step:
+                    rows.append(g.as_strided((2 * g.shape[0],) + tuple(g.shape[1:]), g.stride()))
+                else:
+                    rows.append(torch.cat([g, u], 0))
+            return _stack_or_view(rows)
+
+        gate_up = QuantizedLinear(gu("weight"), gu("scales"), gu("biases"), q.group_size, q.bits, q.mode,
+                                  q.global_scale)
+        d = e0.down_proj
+        down = QuantizedLinear(fuse(lambda e: e.down_proj.weight), fuse(lambda e: e.down_proj.scales),
+                               None if d.biases is None else fuse(lambda e: e.down_proj.biases),
+                               d.group_size, d.bits, d.mode, d.global_scale)
+        return cls(gate_up, down)
+
+    def expert(self, e: int) -> Expert:
+        """Expert e as sliced views, the way `build_moe_experts` hands them out."""
+        gu, dn = self.gate_up, self.down
+        i = gu.weight.shape[1] // 2
+
+        def sl(q: QuantizedLinear, rows) -> QuantizedLinear:
+            return QuantizedLinear(q.weight[e][rows], q.scales[e][rows],
+                                   None if q.biases is None else q.biases[e][rows],
+                                   q.group_size, q.bits, q.mode, q.global_scale)
+
+        return Expert(sl(gu, slice(0, i)), sl(gu, slice(i, 2 * i)), sl(dn, slice(None)))

@@ -1,0 +1,165 @@
+"""End-to-end parity of the MoE block on the GPU (through the C ABI) against the
+CPU checker: bit-exact routing and dispatch on tie-free rows, outputs within
+relative L2 2e-3 of the fp32-accumulated result."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from ironmlx_b200 import _lib, nn
+from ironmlx_b200.workloads import CONFIGS, MoEConfig
+from oracle import formats as F
+from oracle import moe as O
+from gpu_util import bf16_to_np, moe_to_device, t_bf16
+from test_gpu_stages import FORMATS, check_routing
+from util import SMALL, TINY, make_params
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3          # relative L2 of the bf16 output against the fp32-accumulated checker
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def run(cfg, dev, path="auto", x=None, p=None):
+    if p is None:
+        x, p = make_params(cfg)
+    moe = moe_to_device(p, dev, path)
+    y, tr = moe.forward_with_stream(t_bf16(x, dev), trace=True)
+    torch.cuda.synchronize()
+    moe.check_status()
+    return x, p, moe, bf16_to_np(y), {k: v.cpu().numpy() for k, v in tr.items()}
+
+
+def compare(cfg, x, p, y, tr, fast=False):
+    ref = O.moe_forward(x, p, fast_bucket=fast)
+    k = cfg.top_k
+    clear = check_routing(tr["topk_idx"], tr["topk_w"], x, p, k, cfg.norm_topk_prob, p.router_logit_bias)
+    if clear.all():
+        assert np.array_equal(tr["counts"], ref.counts) and np.array_equal(tr["offsets"], ref.offsets)
+        assert np.array_equal(tr["perm"], ref.perm) and np.array_equal(tr["inv_perm"], ref.inv_perm)
+    else:   # the permutation of the GPU's own routing must still be the stable sort
+        c, o, pm, inv = O.bucket_fast(tr["topk_idx"], cfg.num_experts)
+        assert np.array_equal(tr["perm"], pm) and np.array_equal(tr["offsets"], o)
+    err = O.rel_l2(y[clear], ref.y[clear])
+    assert err <= TOL, f"{cfg.name}: rel-L2 {err:.3e} > {TOL}"
+    assert np.abs(y[clear] - ref.y[clear]).max() <= 2 ** -7 * np.abs(ref.y).max() + 1e-6
+    return err
+
+
+@pytest.mark.parametrize("path", ["generic", "decode"])
+@pytest.mark.parametrize("cfg", [TINY, SMALL, CONFIGS["c1"]], ids=lambda c: c.name)
+def test_block_affine4(cuda, cfg, path):
+    x, p, _, y, tr = run(cfg, cuda, path)
+    compare(cfg, x, p, y, tr)
+
+
+def test_c1_against_golden_fixture(cuda):
+    cfg = CONFIGS["c1"]
+    g = np.load(os.path.join(GOLDEN, "c1.npz"))
+    x, p, _, y, tr = run(cfg, cuda)
+    assert np.array_equal(tr["topk_idx"], g["top_idx"]) and np.array_equal(tr["perm"], g["perm"])
+    assert np.array_equal(tr["counts"], g["counts"])
+    assert O.rel_l2(y, g["y"]) <= TOL
+
+
+@pytest.mark.parametrize("mode,bits,group", FORMATS)
+def test_block_every_format(cuda, mode, bits, group):
+    cfg = SMALL.with_(name=f"small-{mode}{bits}g{group}", mode=mode, bits=bits, group_size=group)
+    x, p, _, y, tr = run(cfg, cuda)
+    compare(cfg, x, p, y, tr)
+    name = f"tiny_{mode}{bits}_g{group}.npz"
+    if os.path.exists(os.path.join(GOLDEN, name)):
+        g = np.load(os.path.join(GOLDEN, name))
+        tcfg = TINY.with_(mode=mode, bits=bits, group_size=group)
+        _, _, _, ty, ttr = run(tcfg, cuda)
+        assert np.array_equal(ttr["perm"], g["perm"]) and O.rel_l2(ty, g["y"]) <= TOL
+
+
+@pytest.mark.parametrize("bits,group", [(2, 64), (4, 128), (8, 64), (8, 128)])
+def test_decode_path_other_widths(cuda, bits, group):
+    cfg = MoEConfig(f"dec{bits}g{group}", tokens=40, hidden=256, num_experts=8, top_k=3, intermediate=128,
+                    shared_intermediate=256, bits=bits, group_size=group, seed=9)
+    x, p, _, y, tr = run(cfg, cuda, "decode")
+    compare(cfg, x, p, y, tr)
+    _, _, _, yg, _ = run(cfg, cuda, "generic", x, p)
+    assert O.rel_l2(y, yg) < 1e-3                        # both paths round the same fp32 sums to bf16
+
+
+@pytest.mark.parametrize("cfg", [
+    MoEConfig("no-norm", 9, 256, 8, 2, 128, 128, norm_topk_prob=False, seed=12),
+    MoEConfig("no-shared", 17, 256, 16, 4, 128, 0, seed=13),
+    MoEConfig("k-eq-e", 6, 128, 4, 4, 128, 128, seed=14),
+    MoEConfig("one-token", 1, 256, 8, 2, 128, 128, seed=15),
+    MoEConfig("one-expert", 5, 128, 1, 1, 128, 0, seed=16),
+    MoEConfig("wide-shared", 12, 256, 8, 2, 128, 384, seed=17),
+    MoEConfig("crowded", 100, 128, 2, 2, 128, 128, seed=18),      # 100 rows per expert: many units
+], ids=lambda c: c.name)
+@pytest.mark.parametrize("path", ["generic", "decode"])
+def test_block_edge_shapes(cuda, cfg, path):
+    x, p, _, y, tr = run(cfg, cuda, path)
+    compare(cfg, x, p, y, tr)
+
+
+def test_empty_experts_and_skew(cuda):
+    cfg = MoEConfig("skew", 64, 256, 32, 4, 128, 128, seed=19, zipf_s=1.2, zipf_hot_share=0.2)
+    x, p = make_params(cfg)
+    p.router_logit_bias[:8] = -30.0                                      # eight experts never selected
+    x, p, _, y, tr = run(cfg, cuda, "decode", x, p)
+    assert (tr["counts"][:8] == 0).all() and tr["counts"].max() >= 0.15 * cfg.assignments
+    compare(cfg, x, p, y, tr)
+
+
+def test_zero_tokens_and_errors(cuda):
+    x, p = make_params(TINY)
+    moe = moe_to_device(p, cuda)
+    y = moe.forward_with_stream(torch.empty(0, TINY.hidden, dtype=torch.bfloat16, device=cuda))
+    assert y.shape == (0, TINY.hidden)
+    with pytest.raises(_lib.IronMLXError):
+        moe.forward_with_stream(torch.zeros(2, TINY.hidden + 16, dtype=torch.bfloat16, device=cuda))
+    with pytest.raises(_lib.IronMLXError):
+        moe.forward_with_stream(torch.zeros(2, TINY.hidden, dtype=torch.float32, device=cuda))
+    x3, p3 = make_params(TINY.with_(bits=3, group_size=32))
+    with pytest.raises(_lib.IronMLXError):                             # 3-bit has no decode path
+        moe_to_device(p3, cuda, "decode").forward_with_stream(t_bf16(x3, cuda))
+
+
+def test_batch_shape_and_views(cuda):
+    """[B, L, H] in and out (moe.rs:56-64,182), experts given as per-expert
+    sliced views the way build_moe_experts hands them out (qwen35.rs:661-776)."""
+    cfg = SMALL
+    x, p = make_params(cfg)
+    fused = moe_to_device(p, cuda)
+    experts = [fused._fused.expert(e) for e in range(cfg.num_experts)]
+    moe = nn.MoEMLP(fused.gate, experts, fused.shared_expert, fused.shared_expert_gate, cfg.top_k, True)
+    assert moe._fused.gate_up.weight.data_ptr() == fused._fused.gate_up.weight.data_ptr()   # no copy
+    xd = t_bf16(x, cuda).reshape(4, 12, cfg.hidden)
+    y3 = moe.forward_with_stream(xd)
+    y2 = fused.forward_with_stream(xd.reshape(-1, cfg.hidden))
+    assert y3.shape == xd.shape and torch.equal(y3.reshape(-1, cfg.hidden), y2)
+
+
+def test_reruns_are_bit_identical(cuda):
+    x, p = make_params(CONFIGS["c1"])
+    moe = moe_to_device(p, cuda)
+    xd = t_bf16(x, cuda)
+    ys = [moe.forward_with_stream(xd).clone() for _ in range(3)]
+    assert torch.equal(ys[0], ys[1]) and torch.equal(ys[0], ys[2])
+
+
+def test_host_io_entry_point(cuda):
+    x, p = make_params(SMALL)
+    moe = moe_to_device(p, cuda)
+    xh = t_bf16(x, "cpu").pin_memory()
+    yh = torch.empty_like(xh).pin_memory()
+    moe.forward_host(xh, yh)
+    yd = moe.forward_with_stream(xh.to(cuda))
+    assert torch.equal(yh.to(cuda), yd)
+
+
+def test_c2_reduced_experts(cuda):
+    """The decode benchmark shape with 32 of the 256 experts (the checker
+    finishes in seconds), 64 tokens, top-8, shared expert."""
+    cfg = CONFIGS["c2"].with_(name="c2-e32", num_experts=32)
+    x, p, _, y, tr = run(cfg, cuda)
+    err = compare(cfg, x, p, y, tr)
+    print(f"c2-e32 rel-L2 {err:.3e}")
