@@ -38,7 +38,8 @@ struct Carver {
 struct ForwardWs {
     int32_t* status;      // [8]
     int32_t* sched;       // [kSchedInts]
-    int32_t* n_units;     // [1]
+    int32_t* n_units;     // [4]: total, routed
+    float* partials;      // [kFlagWarps][256] hand-off slots of the decode kernels
     int32_t* topk_idx;    // [A]
     float* topk_w;        // [A]
     float* shared_gate;   // [N]
@@ -71,6 +72,7 @@ ForwardWs carve_forward(const imx_moe_config& c, int n, void* base) {
     w.status = cv.take<int32_t>(8);
     w.sched = cv.take<int32_t>(kSchedInts);
     w.n_units = cv.take<int32_t>(4);
+    w.partials = cv.take<float>((size_t)kFlagWarps * 256);
     w.topk_idx = cv.take<int32_t>(A);
     w.topk_w = cv.take<float>(A);
     w.shared_gate = cv.take<float>(n);
@@ -105,7 +107,7 @@ int check_config(const imx_moe_config* c, QFormat* f) {
                     c->shared_intermediate % 8 == 0,
                 "shared_intermediate (%d) must be a multiple of the group size and of 8", c->shared_intermediate);
     IMX_REQUIRE(c->hidden % f->group == 0, "hidden (%d) must be a multiple of the group size (%d)", c->hidden, f->group);
-    IMX_REQUIRE(c->path >= IMX_PATH_AUTO && c->path <= IMX_PATH_GENERIC, "unknown path %d", c->path);
+    IMX_REQUIRE(c->path >= IMX_PATH_AUTO && c->path <= IMX_PATH_DECODE_REGS, "unknown path %d", c->path);
     return IMX_OK;
 }
 
@@ -170,14 +172,15 @@ int pick_path(const imx_moe_config& c, const ExpertSet& s, int* path) {
     int p = c.path;
     if (p == IMX_PATH_AUTO) p = decode_mma_supported(s) ? IMX_PATH_DECODE : IMX_PATH_GENERIC;
     if (p == IMX_PATH_PREFILL) p = decode_mma_supported(s) ? IMX_PATH_DECODE : IMX_PATH_GENERIC;
-    IMX_REQUIRE(p != IMX_PATH_DECODE || decode_mma_supported(s),
+    IMX_REQUIRE((p != IMX_PATH_DECODE && p != IMX_PATH_DECODE_REGS) || decode_mma_supported(s),
                 "the decode path supports affine 2/4/8-bit, group 64/128, sizes that are multiples of 128");
     *path = p;
     return IMX_OK;
 }
 
 int run_experts(int path, const GroupedArgs& ga, cudaStream_t stream, cudaEvent_t mid = nullptr) {
-    if (path == IMX_PATH_DECODE) return launch_decode_mma(ga, stream, mid);
+    if (path == IMX_PATH_DECODE && decode_tma_supported(ga.set)) return launch_decode_tma(ga, stream, mid);
+    if (path == IMX_PATH_DECODE || path == IMX_PATH_DECODE_REGS) return launch_decode_mma(ga, stream, mid);
     return launch_generic_grouped(ga, stream, mid);
 }
 
@@ -198,16 +201,18 @@ __global__ void build_units_kernel(const int32_t* __restrict__ offsets, int E, i
                 units[n++] = u;
             }
         }
-        *n_units = n;
+        n_units[0] = n;
+        n_units[1] = n;          // no extra expert at this entry point: all units are routed
     }
-    if (sched != nullptr && threadIdx.x < kSchedInts) sched[threadIdx.x] = 0;
+    if (sched != nullptr)
+        for (int i = threadIdx.x; i < kSchedInts; i += blockDim.x) sched[i] = 0;
 }
 
 }  // namespace
 
 int launch_build_units(const int32_t* offsets, int E, int unit_rows, WorkUnit* units, int32_t* n_units,
                        int32_t* sched, cudaStream_t stream) {
-    build_units_kernel<<<1, 32, 0, stream>>>(offsets, E, unit_rows, units, n_units, sched);
+    build_units_kernel<<<1, 256, 0, stream>>>(offsets, E, unit_rows, units, n_units, sched);
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }
@@ -216,6 +221,7 @@ namespace {
 struct ExpertsWs {
     int32_t* sched;
     int32_t* n_units;
+    float* partials;
     WorkUnit* units;
     __half* act;
     __half* xperm;       // activations re-ordered for the decode kernels
@@ -227,6 +233,7 @@ ExpertsWs carve_experts(const imx_moe_config& c, int n_rows, int n_src_rows, voi
     Carver cv(base);
     w.sched = cv.take<int32_t>(kSchedInts);
     w.n_units = cv.take<int32_t>(4);
+    w.partials = cv.take<float>((size_t)kFlagWarps * 256);
     w.max_units = max_units_for(n_rows, c.num_experts, 0);
     w.units = cv.take<WorkUnit>(w.max_units);
     w.act = cv.take<__half>((size_t)n_rows * c.intermediate);
@@ -290,7 +297,7 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
 
     const int A = n_tokens * c.top_k;
     int order[16];
-    decode_block_order(path == IMX_PATH_DECODE ? f.bits : 0, order);
+    decode_block_order((path == IMX_PATH_DECODE || path == IMX_PATH_DECODE_REGS) ? f.bits : 0, order);
     auto mark = [&](int i) -> cudaError_t { return ev ? cudaEventRecord(ev[i], stream) : cudaSuccess; };
     IMX_CHECK_CUDA(mark(0));
     IMX_TRY(launch_route(x, n_tokens, c.hidden, w->router_w, w->router_logit_bias, c.num_experts, c.top_k,
@@ -319,6 +326,7 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     ga.n_units = ws.n_units;
     ga.max_units = ws.max_units;
     ga.sched = ws.sched;
+    ga.partials = ws.partials;
     ga.act = ws.act;
     ga.act_stride = ws.act_stride;
     ga.row_scale = ws.w_of_slot;
@@ -465,7 +473,7 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
     ga.set = set;
     ga.in = (const __half*)x_f16;
     ga.row_index = row_index;
-    if (path == IMX_PATH_DECODE) {
+    if (path == IMX_PATH_DECODE || path == IMX_PATH_DECODE_REGS) {
         // gather the rows once, in the block order the decode kernels read
         int o[16];
         decode_block_order(f.bits, o);
@@ -480,6 +488,7 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
     ga.n_units = ws.n_units;
     ga.max_units = ws.max_units;
     ga.sched = ws.sched;
+    ga.partials = ws.partials;
     ga.act = ws.act;
     ga.act_stride = c.intermediate;
     ga.row_scale = row_scale;

@@ -12,7 +12,8 @@ namespace imx {
 
 namespace {
 
-constexpr int kCThreads = 256;
+constexpr int kCThreads = 128;
+constexpr int kCCols = kCThreads * 4;      // columns per CTA
 constexpr int kMaxK = 64;
 
 __global__ void __launch_bounds__(kCThreads)
@@ -33,25 +34,32 @@ combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ inv_p
         }
     }
     __syncthreads();
-    for (int c = tid * 4; c < H; c += kCThreads * 4) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s = 0; s < k; ++s) {
-            const int slot = s_slot[s];
-            if (slot < 0) continue;              // dropped assignment (moe.rs:100)
-            const float4 v = *reinterpret_cast<const float4*>(rows + (size_t)slot * H + c);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    const int c = blockIdx.y * kCCols + tid * 4;
+    if (c >= H) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < k; s0 += 8) {          // eight independent row loads in flight, added in order
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int slot = (s0 + j < k) ? s_slot[s0 + j] : -1;
+            v[j] = slot >= 0 ? __ldg(reinterpret_cast<const float4*>(rows + (size_t)slot * H + c))
+                             : make_float4(0.f, 0.f, 0.f, 0.f);      // dropped assignment (moe.rs:100)
         }
-        if (shared_rows != nullptr) {
-            const float4 v = *reinterpret_cast<const float4*>(shared_rows + (size_t)t * H + c);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w;
         }
-        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
-        __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
-        uint2 o;
-        o.x = *reinterpret_cast<uint32_t*>(&lo);
-        o.y = *reinterpret_cast<uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(y + (size_t)t * H + c) = o;
     }
+    if (shared_rows != nullptr) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(shared_rows + (size_t)t * H + c));
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(y + (size_t)t * H + c) = o;
 }
 
 }  // namespace
@@ -61,7 +69,8 @@ int launch_combine(const float* rows, const int32_t* inv_perm, int n, int k, int
     IMX_REQUIRE(k >= 1 && k <= kMaxK, "combine: top_k (%d) must be in 1..%d", k, kMaxK);
     IMX_REQUIRE(H % 4 == 0, "combine: hidden (%d) must be a multiple of 4", H);
     if (n == 0) return IMX_OK;
-    combine_kernel<<<n, kCThreads, 0, stream>>>(rows, inv_perm, k, H, shared_rows, (__nv_bfloat16*)y);
+    dim3 grid(n, ceil_div(H, kCCols));
+    combine_kernel<<<grid, kCThreads, 0, stream>>>(rows, inv_perm, k, H, shared_rows, (__nv_bfloat16*)y);
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }

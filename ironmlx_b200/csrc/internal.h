@@ -22,7 +22,11 @@ struct Order16 {
     int8_t o[16];
 };
 
-constexpr int kSchedInts = 8;      // work-stealing counters cleared by the sort stage
+// Ints cleared by the sort stage before every pass of the expert kernels:
+// [0, 8) scheduler counters, then one "partial ready" flag per warp of the two
+// decode kernels (stream-K hand-off), kFlagWarps each.
+constexpr int kFlagWarps = 4096;
+constexpr int kSchedInts = 8 + 2 * kFlagWarps;
 constexpr int kUnitRows = 8;       // slots per decode work unit (the n=8 side of the MMA)
 
 struct SortExtras {
@@ -79,7 +83,8 @@ struct GroupedArgs {
     const WorkUnit* units;
     const int32_t* n_units;
     int max_units;
-    int32_t* sched;                // [kSchedInts]; decode kernels use [0] and [1]
+    int32_t* sched;                // [kSchedInts]: counters, then the hand-off flags
+    float* partials;               // [kFlagWarps][8][32] fp32 hand-off slots (decode kernels)
     __half* act;                   // fp16 [n_slots, act_stride]
     int act_stride;
     const float* row_scale;        // per slot or nullptr
@@ -90,6 +95,8 @@ struct GroupedArgs {
 bool decode_mma_supported(const ExpertSet& s);
 // `mid`, when given, is recorded between the first and the second product.
 int launch_decode_mma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
+bool decode_tma_supported(const ExpertSet& s);
+int launch_decode_tma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 int launch_generic_grouped(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 
 int launch_combine(const float* rows, const int32_t* inv_perm, int n, int k, int H,

@@ -137,30 +137,47 @@ route_kernel(const __nv_bfloat16* __restrict__ x, int H, const __nv_bfloat16* __
     const int e_hi = min(E, e_lo + per);
     // the last CTA of the cluster also owns the shared-gate dot product (index E)
     const int n_rows = (e_hi - e_lo) + ((rank == cs - 1 && w_sg != nullptr) ? 1 : 0);
-    for (int r = warp; r < n_rows; r += nwarps) {
-        const bool is_gate = (e_lo + r >= e_hi);
-        const __nv_bfloat16* wrow = is_gate ? w_sg : Wr + (size_t)(e_lo + r) * H;
-        float acc = 0.f;
+    // Each warp takes kRowsPerPass weight rows at a time so that their loads
+    // are independent and in flight together (the stage is latency-bound).
+    constexpr int kRowsPerPass = 4;
+    for (int r0 = warp * kRowsPerPass; r0 < n_rows; r0 += nwarps * kRowsPerPass) {
+        const __nv_bfloat16* wrow[kRowsPerPass];
+        float acc[kRowsPerPass];
+#pragma unroll
+        for (int j = 0; j < kRowsPerPass; ++j) {
+            const int r = min(r0 + j, n_rows - 1);           // clamp: duplicates are discarded below
+            wrow[j] = (e_lo + r >= e_hi) ? w_sg : Wr + (size_t)(e_lo + r) * H;
+            acc[j] = 0.f;
+        }
+#pragma unroll 4
         for (int c = lane * 8; c < H; c += 256) {
-            uint4 wv = *reinterpret_cast<const uint4*>(wrow + c);
-            uint4 xv = *reinterpret_cast<const uint4*>(s_x + c);
-            const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+            uint4 wv[kRowsPerPass];
+#pragma unroll
+            for (int j = 0; j < kRowsPerPass; ++j) wv[j] = __ldg(reinterpret_cast<const uint4*>(wrow[j] + c));
+            const uint4 xv = *reinterpret_cast<const uint4*>(s_x + c);
             const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float2 wf = __bfloat1622float2(wb[i]);
-                float2 xf = __bfloat1622float2(xb[i]);
-                acc = fmaf(wf.x, xf.x, acc);
-                acc = fmaf(wf.y, xf.y, acc);
+            for (int j = 0; j < kRowsPerPass; ++j) {
+                const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv[j]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 wf = __bfloat1622float2(wb[i]);
+                    const float2 xf = __bfloat1622float2(xb[i]);
+                    acc[j] = fmaf(wf.x, xf.x, acc[j]);
+                    acc[j] = fmaf(wf.y, xf.y, acc[j]);
+                }
             }
         }
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            if (is_gate) {
-                shared_gate[token] = 1.0f / (1.0f + expf(-acc));
-            } else {
-                if (logit_bias != nullptr) acc += logit_bias[e_lo + r];
-                leader_logits[e_lo + r] = acc;
+#pragma unroll
+        for (int j = 0; j < kRowsPerPass; ++j) {
+            const float v = warp_sum(acc[j]);
+            const int r = r0 + j;
+            if (lane == 0 && r < n_rows) {
+                if (e_lo + r >= e_hi) {
+                    shared_gate[token] = 1.0f / (1.0f + expf(-v));
+                } else {
+                    leader_logits[e_lo + r] = v + (logit_bias != nullptr ? logit_bias[e_lo + r] : 0.f);
+                }
             }
         }
     }

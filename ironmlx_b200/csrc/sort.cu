@@ -140,7 +140,8 @@ struct SortAux {
 __device__ void emit_aux(const SortAux& aux, const int32_t* __restrict__ perm, const int* s_off,
                          int E, int A, int* s_warp) {
     const int tid = threadIdx.x;
-    if (aux.sched != nullptr && tid < kSchedInts) aux.sched[tid] = 0;
+    if (aux.sched != nullptr)
+        for (int i = tid; i < kSchedInts; i += kSortThreads) aux.sched[i] = 0;
     if (aux.tok_of_slot != nullptr) {
         const int total = s_off[E];
         for (int j = tid; j < total; j += kSortThreads) {
@@ -178,7 +179,8 @@ __device__ void emit_aux(const SortAux& aux, const int32_t* __restrict__ perm, c
             u.pad = 0;
             aux.units[base + c] = u;
         }
-        if (tid == 0) *aux.n_units = total;
+        if (tid == 0) aux.n_units[0] = total;
+        if (tid == E) aux.n_units[1] = base;       // units of the routed experts (the extra expert's follow)
     }
 }
 

@@ -198,10 +198,11 @@ def nvfp4_quantize(w, group_size: int = 16, with_global_scale: bool = True):
 def nvfp4_dequantize(w, scales, group_size: int = 16, global_scale=1.0) -> np.ndarray:
     nib = unpack_bits(w, 4)
     v = e2m1_to_f32(nib)
-    s = e4m3_to_f32(scales) * np.float32(global_scale)
+    s = e4m3_to_f32(scales)
     n = v.shape[-1]
     vg = v.reshape(v.shape[:-1] + (n // group_size, group_size))
-    return (vg * s[..., None]).reshape(v.shape).astype(np.float32)
+    # value x block scale is exact in fp32 (2 + 4 significant bits); one rounding with the tensor scale
+    return ((vg * s[..., None]) * np.float32(global_scale)).reshape(v.shape).astype(np.float32)
 
 
 # ── the reference's two quantized ops (mlx/src/ops.rs:653-727) ──────────────

@@ -129,6 +129,8 @@ def routing_margin(probs: np.ndarray, k: int) -> np.ndarray:
     descending top-(k+1) probabilities.  Rows whose margin is far above fp32
     rounding noise have one and only one correct (ordered) expert list."""
     srt = -np.sort(-probs.astype(np.float64), axis=-1)[:, : k + 1]
+    if srt.shape[1] < 2:
+        return np.full(probs.shape[0], np.inf)
     gaps = (srt[:, :-1] - srt[:, 1:]) / srt[:, :-1]
     return gaps.min(-1)
 

@@ -46,7 +46,7 @@ def compare(cfg, x, p, y, tr, fast=False):
     return err
 
 
-@pytest.mark.parametrize("path", ["generic", "decode"])
+@pytest.mark.parametrize("path", ["generic", "decode", "decode_regs"])
 @pytest.mark.parametrize("cfg", [TINY, SMALL, CONFIGS["c1"]], ids=lambda c: c.name)
 def test_block_affine4(cuda, cfg, path):
     x, p, _, y, tr = run(cfg, cuda, path)
@@ -94,7 +94,7 @@ def test_decode_path_other_widths(cuda, bits, group):
     MoEConfig("wide-shared", 12, 256, 8, 2, 128, 384, seed=17),
     MoEConfig("crowded", 100, 128, 2, 2, 128, 128, seed=18),      # 100 rows per expert: many units
 ], ids=lambda c: c.name)
-@pytest.mark.parametrize("path", ["generic", "decode"])
+@pytest.mark.parametrize("path", ["generic", "decode", "decode_regs"])
 def test_block_edge_shapes(cuda, cfg, path):
     x, p, _, y, tr = run(cfg, cuda, path)
     compare(cfg, x, p, y, tr)

@@ -67,7 +67,10 @@ def test_route_matches_checker(cuda, cfg):
         p.shared_expert_gate_w = wl.shared_gate_weight().astype(F.bf16)
     idx, w, sg, x16 = run_route(x, p, cfg.top_k, cfg.norm_topk_prob, cuda)
     check_routing(idx, w, x, p, cfg.top_k, cfg.norm_topk_prob)
-    assert np.array_equal(x16.astype(np.float32), x)            # fp16 copy is exact for these inputs
+    # the fp16 copy is exact except below fp16's subnormal spacing (2^-24)
+    big = np.abs(x) >= 2.0 ** -14
+    assert np.array_equal(x16.astype(np.float32)[big], x[big])
+    assert np.abs(x16.astype(np.float32) - x).max() <= 2.0 ** -25
     if cfg.shared_intermediate:
         ref = O.sigmoid((x.astype(np.float64) @ p.shared_expert_gate_w.astype(np.float32).astype(np.float64).T)
                         .astype(np.float32))[:, 0]
