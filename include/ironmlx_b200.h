@@ -190,6 +190,19 @@ IMX_API int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_u
 IMX_API int imx_moe_combine(const float* rows, const int32_t* inv_perm, int n_tokens, int top_k,
                     int hidden, const float* shared_rows, void* y, void* stream);
 
+/* The same combine for rows that arrive UNWEIGHTED (expert parallelism: the
+ * rows come back from the ranks that own the experts): every row is first
+ * multiplied by row_scale[slot] in fp32 (moe.rs:155-161), then added as above. */
+IMX_API int imx_moe_combine_scaled(const float* rows, const float* row_scale, const int32_t* inv_perm,
+                           int n_tokens, int top_k, int hidden, const float* shared_rows, void* y,
+                           void* stream);
+
+/* dst[j, :] = src[index[j], :], rows of row_bytes bytes (a multiple of 4): the
+ * `take_axis` of moe.rs:124-127, used to pack the dispatch and return buffers
+ * of the expert-parallel exchange. */
+IMX_API int imx_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,
+                    void* stream);
+
 /* ── the reference's quantized-op surface, mlx/src/ops.rs:630-727 ──────── */
 
 /* out[rows, in] = dequantize(w) (ops.rs:653-686 -> mlx_dequantize).

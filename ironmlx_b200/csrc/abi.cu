@@ -334,7 +334,7 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     ga.status = ws.status;
     IMX_TRY(run_experts(path, ga, stream, ev ? ev[3] : nullptr));
     IMX_CHECK_CUDA(mark(4));
-    IMX_TRY(launch_combine(ws.rows, ws.inv_perm, n_tokens, c.top_k, c.hidden,
+    IMX_TRY(launch_combine(ws.rows, nullptr, ws.inv_perm, n_tokens, c.top_k, c.hidden,
                            has_shared ? ws.rows + (size_t)A * c.hidden : nullptr, y, stream));
     IMX_CHECK_CUDA(mark(5));
     if (trace != nullptr) {
@@ -502,7 +502,22 @@ int imx_moe_combine(const float* rows, const int32_t* inv_perm, int n_tokens, in
     IMX_REQUIRE(n_tokens >= 0, "combine: negative token count");
     if (n_tokens == 0) return IMX_OK;
     IMX_REQUIRE(rows && inv_perm && y, "combine: rows, inv_perm and y are required");
-    return launch_combine(rows, inv_perm, n_tokens, top_k, hidden, shared_rows, y, (cudaStream_t)stream);
+    return launch_combine(rows, nullptr, inv_perm, n_tokens, top_k, hidden, shared_rows, y, (cudaStream_t)stream);
+}
+
+int imx_moe_combine_scaled(const float* rows, const float* row_scale, const int32_t* inv_perm, int n_tokens,
+                           int top_k, int hidden, const float* shared_rows, void* y, void* stream) {
+    IMX_REQUIRE(n_tokens >= 0, "combine: negative token count");
+    if (n_tokens == 0) return IMX_OK;
+    IMX_REQUIRE(rows && row_scale && inv_perm && y, "combine_scaled: rows, row_scale, inv_perm and y are required");
+    return launch_combine(rows, row_scale, inv_perm, n_tokens, top_k, hidden, shared_rows, y, (cudaStream_t)stream);
+}
+
+int imx_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst, void* stream) {
+    IMX_REQUIRE(n_rows >= 0, "gather_rows: negative row count");
+    if (n_rows == 0) return IMX_OK;
+    IMX_REQUIRE(src && index && dst, "gather_rows: src, index and dst are required");
+    return launch_gather_rows(src, index, n_rows, row_bytes, dst, (cudaStream_t)stream);
 }
 
 int imx_dequantize(const imx_qtensor* w, int rows, int in, int group_size, int bits, int mode, int out_dtype,

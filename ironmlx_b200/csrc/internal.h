@@ -99,8 +99,10 @@ bool decode_tma_supported(const ExpertSet& s);
 int launch_decode_tma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 int launch_generic_grouped(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 
-int launch_combine(const float* rows, const int32_t* inv_perm, int n, int k, int H,
+int launch_combine(const float* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,
                    const float* shared_rows, void* y, cudaStream_t stream);
+int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,
+                       cudaStream_t stream);
 
 // Builds the unit list for a caller-given offsets array (stage-level API).
 int launch_build_units(const int32_t* offsets, int E, int unit_rows, WorkUnit* units, int32_t* n_units,

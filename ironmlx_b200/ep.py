@@ -1,0 +1,294 @@
+"""Expert parallelism for the MoE block: one process per GPU, the E experts
+split into contiguous blocks of E/R per rank, tokens sharded across ranks, and
+one all-to-all each way (dispatch of activation rows to the ranks that own
+their experts, return of the expert outputs) over torch.distributed (NCCL on
+NVLink).  The reference has no distributed code at all (no collective, no
+communicator anywhere in its tree); single-device results are what this has to
+reproduce.
+
+Per step and rank (n local tokens, k experts per token):
+
+  1. route + sort locally over the GLOBAL expert ids: because every rank owns
+     a contiguous block of experts, the stable sort by expert id is already
+     grouped by destination rank, then by expert, then by flat index.
+  2. counts: an all-to-all of the [R, E/R] count matrix tells every rank how
+     many rows it receives from each source for each of its experts; the two
+     count matrices come to the host once per step (the split sizes of the
+     all-to-all-v are host values).
+  3. dispatch: fp16 activation rows gathered in sorted order -> all-to-all-v.
+  4. local experts: received rows are ordered (source, expert); a second stable
+     sort by local expert id gives the grouped order the expert kernels want.
+  5. return: outputs (fp32, unweighted) put back in received order -> all-to-all-v.
+  6. combine on the source rank: rows scaled by their routing weight and added
+     per token in ascending expert order, plus the local gated shared expert
+     (replicated weights, computed on a side stream under the exchanges).
+
+The stage kernels come from a `stages` object (the C ABI on CUDA tensors in
+production; the tests substitute a CPU implementation to run the bookkeeping
+on gloo ranks).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, nn, ops
+from ._lib import MoEConfig, check, lib
+
+
+class CudaStages:
+    """The stage-level C ABI calls on torch CUDA tensors."""
+
+    def __init__(self, device):
+        self.device = device
+        self._scratch = {}
+
+    def _buf(self, key, nbytes):
+        b = self._scratch.get(key)
+        if b is None or b.numel() < nbytes:
+            b = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=self.device)
+            self._scratch[key] = b
+        return b
+
+    def route(self, x, router_w, logit_bias, k, norm, shared_gate_w):
+        n, h = x.shape
+        e = router_w.shape[0]
+        idx = torch.empty(n, k, dtype=torch.int32, device=x.device)
+        w = torch.empty(n, k, dtype=torch.float32, device=x.device)
+        sg = torch.empty(n, dtype=torch.float32, device=x.device)
+        x16 = torch.empty(n, h, dtype=torch.float16, device=x.device)
+        check(lib().imx_moe_route(x.data_ptr(), n, h, router_w.data_ptr(),
+                                  None if logit_bias is None else logit_bias.data_ptr(), e, k, int(norm),
+                                  None if shared_gate_w is None else shared_gate_w.data_ptr(), idx.data_ptr(),
+                                  w.data_ptr(), sg.data_ptr(), x16.data_ptr(), ops.stream_ptr()))
+        return idx, w, sg, x16
+
+    def sort(self, ids, num_experts):
+        a = ids.numel()
+        i32 = dict(dtype=torch.int32, device=ids.device)
+        counts, offsets = torch.empty(num_experts, **i32), torch.empty(num_experts + 1, **i32)
+        perm, inv = torch.empty(max(a, 1), **i32), torch.empty(max(a, 1), **i32)
+        nb = C.c_size_t(0)
+        check(lib().imx_moe_sort_scratch_bytes(a, num_experts, C.byref(nb)))
+        scratch = self._buf("sort", nb.value)
+        check(lib().imx_moe_sort(ids.data_ptr(), a, num_experts, counts.data_ptr(), offsets.data_ptr(),
+                                 perm.data_ptr(), inv.data_ptr(), scratch.data_ptr(), scratch.numel(),
+                                 ops.stream_ptr()))
+        return counts, offsets, perm[:a], inv[:a]
+
+    def gather_rows(self, src, index):
+        n = index.numel()
+        src2 = src.reshape(src.shape[0], -1)
+        out = torch.empty((n,) + tuple(src2.shape[1:]), dtype=src.dtype, device=src.device)
+        row_bytes = src2.shape[1] * src.element_size()
+        check(lib().imx_gather_rows(src2.data_ptr(), index.data_ptr(), n, row_bytes, out.data_ptr(),
+                                    ops.stream_ptr()))
+        return out
+
+    def experts(self, cfg: MoEConfig, gate_up: nn.QuantizedLinear, down: nn.QuantizedLinear, num_experts,
+                x16, row_index, offsets, n_rows, row_scale, key="experts"):
+        out = torch.empty(n_rows, cfg.hidden, dtype=torch.float32, device=x16.device)
+        if n_rows == 0:
+            return out
+        nb = C.c_size_t(0)
+        check(lib().imx_moe_experts_scratch_bytes(C.byref(cfg), n_rows, C.byref(nb)))
+        scratch = self._buf(key, nb.value)
+        g, d = gate_up.qtensor(), down.qtensor()
+        check(lib().imx_moe_experts(C.byref(cfg), C.byref(g), C.byref(d), num_experts, x16.data_ptr(),
+                                    None if row_index is None else row_index.data_ptr(), offsets.data_ptr(),
+                                    n_rows, n_rows, None if row_scale is None else row_scale.data_ptr(),
+                                    out.data_ptr(), scratch.data_ptr(), scratch.numel(), ops.stream_ptr()))
+        return out
+
+    def combine_scaled(self, rows, row_scale, inv_perm, n, k, hidden, shared_rows):
+        y = torch.empty(n, hidden, dtype=torch.bfloat16, device=rows.device)
+        check(lib().imx_moe_combine_scaled(rows.data_ptr(), row_scale.data_ptr(), inv_perm.data_ptr(), n, k, hidden,
+                                           None if shared_rows is None else shared_rows.data_ptr(), y.data_ptr(),
+                                           ops.stream_ptr()))
+        return y
+
+
+@dataclass
+class LocalExperts:
+    """The weights one rank holds: its block of routed experts (fused layout)
+    and, replicated on every rank, the router, the shared expert (gate and up
+    rows fused once into [1, 2*Is, .]) and the shared-expert gate."""
+    router_w: torch.Tensor
+    gate_up: nn.QuantizedLinear        # [E/R, 2I, .]
+    down: nn.QuantizedLinear           # [E/R, H, .]
+    shared_gate_up: Optional[nn.QuantizedLinear] = None   # [1, 2Is, .]
+    shared_down: Optional[nn.QuantizedLinear] = None      # [1, H, .]
+    shared_expert_gate_w: Optional[torch.Tensor] = None
+    router_logit_bias: Optional[torch.Tensor] = None
+
+
+def fuse_shared(mlp: nn.MLP):
+    """gate_proj/up_proj [Is, .] -> one [1, 2Is, .] tensor; down -> [1, H, .]."""
+    g, u, d = mlp.gate_proj, mlp.up_proj, mlp.down_proj
+    cat = lambda a, b: None if a is None else torch.cat([a, b], 0).unsqueeze(0).contiguous()
+    gu = nn.QuantizedLinear(cat(g.weight, u.weight), cat(g.scales, u.scales), cat(g.biases, u.biases),
+                            g.group_size, g.bits, g.mode, g.global_scale)
+    dn = nn.QuantizedLinear(d.weight.unsqueeze(0).contiguous(), d.scales.unsqueeze(0).contiguous(),
+                            None if d.biases is None else d.biases.unsqueeze(0).contiguous(),
+                            d.group_size, d.bits, d.mode, d.global_scale)
+    return gu, dn
+
+
+def validate_counts(send_cnt: torch.Tensor, recv_cnt: torch.Tensor, n_assign: int, world: int, e_local: int):
+    """Host-side checks on the count matrices before any data moves; a mismatch
+    here means a rank disagrees about the exchange and must not reach NCCL."""
+    if tuple(send_cnt.shape) != (world, e_local) or tuple(recv_cnt.shape) != (world, e_local):
+        raise _lib.IronMLXError(_lib.ERR_INVALID, "expert-parallel count matrix has the wrong shape")
+    if int(send_cnt.min()) < 0 or int(recv_cnt.min()) < 0:
+        raise _lib.IronMLXError(_lib.ERR_INVALID, "negative count in the expert-parallel exchange")
+    if int(send_cnt.sum()) != n_assign:
+        raise _lib.IronMLXError(_lib.ERR_INVALID,
+                                f"dispatch counts sum to {int(send_cnt.sum())}, expected {n_assign} assignments")
+
+
+class ExpertParallelMoE:
+    def __init__(self, stages, weights: LocalExperts, num_experts: int, top_k: int, norm_topk_prob: bool,
+                 hidden: int, intermediate: int, shared_intermediate: int, group=None, path: str = "auto"):
+        self.st = stages
+        self.w = weights
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if num_experts % self.world:
+            raise _lib.IronMLXError(_lib.ERR_INVALID, "num_experts must be divisible by the number of ranks")
+        self.E, self.k, self.norm = num_experts, top_k, norm_topk_prob
+        self.E_loc = num_experts // self.world
+        self.H, self.I, self.Is = hidden, intermediate, shared_intermediate
+        q = weights.gate_up
+        mk = lambda inter, ne: MoEConfig(hidden, ne, 1, inter, 0, 1, _lib.MODE[q.mode], q.bits, q.group_size,
+                                         _lib.PATH[path])
+        self.cfg_routed = mk(intermediate, self.E_loc)
+        self.cfg_shared = mk(shared_intermediate, 1) if shared_intermediate else None
+        self.side_stream = (torch.cuda.Stream()
+                            if torch.cuda.is_available() and getattr(weights.router_w, "is_cuda", False) else None)
+        self.last = {}
+
+    # -- collectives -----------------------------------------------------------
+    def _a2a(self, send, out_rows: int, in_splits: List[int], out_splits: List[int]):
+        recv = torch.empty((out_rows,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+        dist.all_to_all_single(recv, send, output_split_sizes=out_splits, input_split_sizes=in_splits,
+                               group=self.group)
+        return recv
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        st, w = self.st, self.w
+        n = x.shape[0]
+        a = n * self.k
+        dev = x.device
+        idx, tw, sg, x16 = st.route(x, w.router_w, w.router_logit_bias, self.k, self.norm, w.shared_expert_gate_w)
+
+        # shared expert: local tokens, replicated weights, off the critical path
+        shared_rows = None
+        if self.Is:
+            off = torch.tensor([0, n], dtype=torch.int32, device=dev)
+            if self.side_stream is not None:
+                self.side_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self.side_stream):
+                    shared_rows = st.experts(self.cfg_shared, w.shared_gate_up, w.shared_down, 1, x16, None, off, n,
+                                             sg, key="shared")
+            else:
+                shared_rows = st.experts(self.cfg_shared, w.shared_gate_up, w.shared_down, 1, x16, None, off, n, sg,
+                                         key="shared")
+
+        counts, offsets, perm, inv = st.sort(idx.reshape(-1), self.E)
+        send_cnt = counts.view(self.world, self.E_loc).contiguous()
+        recv_cnt = torch.empty_like(send_cnt)
+        dist.all_to_all_single(recv_cnt, send_cnt, group=self.group)
+        both = torch.stack([send_cnt, recv_cnt]).cpu()                    # the one host sync of the step
+        validate_counts(both[0], both[1], a, self.world, self.E_loc)
+        in_splits = both[0].sum(1).tolist()
+        out_splits = both[1].sum(1).tolist()
+        n_recv = int(sum(out_splits))
+
+        tok = torch.div(perm, self.k, rounding_mode="floor").to(torch.int32)
+        send_rows = st.gather_rows(x16, tok)
+        recv_rows = self._a2a(send_rows, n_recv, in_splits, out_splits)
+
+        # received rows are ordered (source rank, local expert): regroup by expert
+        ids = torch.repeat_interleave(torch.arange(self.E_loc, dtype=torch.int32, device=dev).repeat(self.world),
+                                      recv_cnt.reshape(-1).to(torch.int64), output_size=n_recv).to(torch.int32)
+        _, off2, perm2, inv2 = st.sort(ids, self.E_loc)
+        out_sorted = st.experts(self.cfg_routed, w.gate_up, w.down, self.E_loc, recv_rows, perm2, off2, n_recv, None)
+        back = st.gather_rows(out_sorted, inv2) if n_recv else out_sorted
+        ret_rows = self._a2a(back, a, out_splits, in_splits)
+
+        w_sorted = st.gather_rows(tw.reshape(-1, 1), perm).reshape(-1)
+        if self.side_stream is not None and shared_rows is not None:
+            torch.cuda.current_stream().wait_stream(self.side_stream)
+        y = st.combine_scaled(ret_rows, w_sorted, inv, n, self.k, self.H, shared_rows)
+        self.last = {"topk_idx": idx, "topk_w": tw, "perm": perm, "counts": counts, "n_recv": n_recv,
+                     "a2a_bytes": (sum(in_splits) - in_splits[self.rank]) * self.H * 2
+                     + (sum(out_splits) - out_splits[self.rank]) * self.H * 4}
+        return y
+
+
+# ── synthetic construction + the benchmark's runner ──────────────────────────
+
+def build_local(cfg, device, rank: int, world: int) -> LocalExperts:
+    """This rank's weights of a seeded synthetic configuration (GPU quantizer)."""
+    from . import synthetic
+    from .workloads import Workload
+    wl = Workload(cfg)
+    e_loc = cfg.num_experts // world
+    lo = rank * e_loc
+    gscale = None
+    if cfg.mode == "nvfp4":
+        raise _lib.IronMLXError(_lib.ERR_INVALID, "nvfp4 tensor scales need the whole tensor: not wired for EP yet")
+    gate_up = synthetic._quantize_stack(lambda e: wl.expert_gate_up(lo + e), e_loc, cfg, device)
+    down = synthetic._quantize_stack(lambda e: wl.expert_down(lo + e), e_loc, cfg, device)
+    out = LocalExperts(synthetic._bf16(wl.router_weight(), device), gate_up, down)
+    if cfg.shared_intermediate:
+        mlp = nn.MLP(*(synthetic._single(synthetic._quantize_stack(lambda e, nm=nm: wl.shared(nm), 1, cfg, device))
+                       for nm in ("gate_proj", "up_proj", "down_proj")))
+        out.shared_gate_up, out.shared_down = fuse_shared(mlp)
+        out.shared_expert_gate_w = synthetic._bf16(wl.shared_gate_weight(), device)
+    bias = wl.router_logit_bias()
+    if bias is not None:
+        out.router_logit_bias = torch.from_numpy(bias).to(device)
+    return out
+
+
+class BenchRunner:
+    """What bench.py drives at N > 1: `cfg.tokens` tokens per rank (weak scaling),
+    experts split across the ranks."""
+
+    launches_per_step = 12
+
+    def __init__(self, cfg, device, rank, world):
+        from .workloads import Workload
+        self.cfg = cfg
+        self.moe = ExpertParallelMoE(CudaStages(device), build_local(cfg, device, rank, world), cfg.num_experts,
+                                     cfg.top_k, cfg.norm_topk_prob, cfg.hidden, cfg.intermediate,
+                                     cfg.shared_intermediate)
+        x = Workload(cfg).activations(block=rank)
+        self.x = torch.from_numpy(x).to(device).to(torch.bfloat16)
+        self.xh = self.x.cpu().pin_memory()
+        self.yh = torch.empty_like(self.xh).pin_memory()
+        self.xd = torch.empty_like(self.x)
+
+    def step(self):
+        return self.moe.forward(self.x)
+
+    def step_host(self):
+        self.xd.copy_(self.xh, non_blocking=True)
+        y = self.moe.forward(self.xd)
+        self.yh.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def extra(self):
+        return {"ep": {"experts_per_rank": self.moe.E_loc, "tokens_per_rank": self.cfg.tokens,
+                       "a2a_bytes_per_rank_per_step": int(self.moe.last.get("a2a_bytes", 0)),
+                       "exchange": "NCCL all_to_all_single (dispatch fp16 rows, return fp32 rows) + count all-to-all"}}
+
+
+def build_bench_runner(cfg, device, rank, world) -> BenchRunner:
+    return BenchRunner(cfg, device, rank, world)
