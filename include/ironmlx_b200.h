@@ -168,6 +168,22 @@ IMX_API int imx_moe_sort(const int32_t* expert_ids, int n_assign, int num_expert
                  int32_t* offsets, int32_t* perm, int32_t* inv_perm, void* scratch,
                  size_t scratch_bytes, void* stream);
 
+/* The same sort for callers that cannot hand over scratch memory or allocate
+ * any.  (No counterpart in the reference: it exists for hosts such as an
+ * inference engine thread that runs under a framework-owned memory cap, where
+ * every device byte must come from that framework's allocator and a stray
+ * cudaMalloc is off limits, or code running at a point where allocating is not
+ * permitted at all.)  The scratch is a fixed 256 KB array inside the library's
+ * device image, so: at most 262144 ids per call (larger inputs are refused with
+ * an error: use imx_moe_sort); the FIRST call on each device looks up the
+ * array's device address (one cudaGetSymbolAddress with that device current) and
+ * should therefore happen before any stream capture begins; all calls on a
+ * device share the one array, so two calls whose kernels can overlap on the GPU
+ * (different streams) race: serialise them.  Nothing in the array needs
+ * clearing between calls.  Calls no cudaMalloc/cudaFree. */
+IMX_API int imx_moe_sort_static(const int32_t* expert_ids, int n_assign, int num_experts, int32_t* counts,
+                        int32_t* offsets, int32_t* perm, int32_t* inv_perm, void* stream);
+
 /* Grouped SwiGLU experts (moe.rs:117-131 with Expert::forward, moe.rs:26-32),
  * a gather_qmm-style call: for every expert e and every sorted slot
  * j in [offsets[e], offsets[e+1]):

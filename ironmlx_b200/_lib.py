@@ -54,6 +54,7 @@ SIGNATURES = {
     "imx_moe_route": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "imx_moe_sort_scratch_bytes": (_i, [_i, _i, C.POINTER(_sz)]),
     "imx_moe_sort": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "imx_moe_sort_static": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "imx_moe_experts_scratch_bytes": (_i, [C.POINTER(MoEConfig), _i, C.POINTER(_sz)]),
     "imx_moe_experts": (_i, [C.POINTER(MoEConfig), C.POINTER(QTensor), C.POINTER(QTensor), _i, _vp, _vp, _vp,
                              _i, _i, _vp, _vp, _vp, _sz, _vp]),

@@ -437,6 +437,14 @@ int imx_moe_sort(const int32_t* expert_ids, int n_assign, int num_experts, int32
                        scratch_bytes, nullptr, (cudaStream_t)stream);
 }
 
+int imx_moe_sort_static(const int32_t* expert_ids, int n_assign, int num_experts, int32_t* counts,
+                        int32_t* offsets, int32_t* perm, int32_t* inv_perm, void* stream) {
+    IMX_REQUIRE(n_assign >= 0 && (n_assign == 0 || expert_ids != nullptr), "sort_static: expert_ids is required");
+    IMX_REQUIRE(offsets && perm && inv_perm, "sort_static: offsets, perm and inv_perm are required");
+    return launch_sort_static(expert_ids, n_assign, num_experts, counts, offsets, perm, inv_perm,
+                              (cudaStream_t)stream);
+}
+
 int imx_moe_experts_scratch_bytes(const imx_moe_config* cfg, int n_rows, size_t* bytes) {
     QFormat f;
     IMX_TRY(check_config(cfg, &f));

@@ -55,6 +55,9 @@ int launch_sort(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offs
                 int32_t* inv_perm, void* scratch, size_t scratch_bytes, const SortExtras* ex,
                 cudaStream_t stream);
 
+int launch_sort_static(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offsets, int32_t* perm,
+                       int32_t* inv_perm, cudaStream_t stream);
+
 // Weights of the experts seen by the grouped kernels: `num_experts` stacked
 // matrices plus one optional extra "expert" (id == num_experts) with its own
 // pointers (the shared expert, whose gate and up projections are separate

@@ -13,6 +13,8 @@
 // Small inputs (decode) run the three steps in ONE single-block kernel that
 // also emits the per-slot gather/scale arrays and the work-unit list of the
 // expert kernels; large inputs use three launches.
+#include <mutex>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -282,6 +284,42 @@ sort_place_kernel(const int32_t* __restrict__ ids, int A, int E, const int32_t* 
 }
 
 }  // namespace
+
+// ── allocation-free variant ─────────────────────────────────────────────────
+// Scratch of the multi-block path for callers that cannot provide any: a fixed
+// array that lives in the library's device image (every GPU that loads the
+// library holds these 256 KB until the process exits).
+constexpr int kStaticSortMaxAssign = 262144;                                   // ids per call
+constexpr int kStaticSortInts = (kStaticSortMaxAssign / kSortChunk) * 1024;    // blocks x experts
+static __device__ __align__(256) int32_t g_sort_scratch[kStaticSortInts];
+
+int launch_sort_static(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offsets, int32_t* perm,
+                       int32_t* inv_perm, cudaStream_t stream) {
+    IMX_REQUIRE(A >= 0 && A <= kStaticSortMaxAssign,
+                "sort_static: %d assignments exceed the built-in scratch (maximum %d); use imx_moe_sort with a "
+                "caller-provided scratch buffer", A, kStaticSortMaxAssign);
+    IMX_REQUIRE(E >= 1 && E <= 1024, "sort_static: num_experts (%d) must be in 1..1024", E);
+    // The array's name is only a host-side handle; kernels need its device
+    // address, looked up once per device with that device current.
+    static std::mutex mu;
+    static void* addr[64] = {};
+    int dev = 0;
+    IMX_CHECK_CUDA(cudaGetDevice(&dev));
+    IMX_REQUIRE(dev >= 0 && dev < 64, "sort_static: device ordinal %d not supported", dev);
+    void* ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (addr[dev] == nullptr) {
+            void* p = nullptr;
+            IMX_CHECK_CUDA(cudaGetSymbolAddress(&p, g_sort_scratch));
+            addr[dev] = p;
+        }
+        ptr = addr[dev];
+    }
+    // every (block, expert) count the later passes read is written by the first pass: nothing to clear
+    return launch_sort(ids, A, E, counts, offsets, perm, inv_perm, ptr, sizeof(int32_t) * kStaticSortInts, nullptr,
+                       stream);
+}
 
 size_t sort_scratch_bytes(int n_assign, int E) {
     int nb = ceil_div(n_assign > 0 ? n_assign : 1, kSortChunk);
