@@ -167,11 +167,17 @@ int make_expert_set(const imx_moe_config& c, const QFormat& f, const imx_qtensor
     return IMX_OK;
 }
 
-// Which expert kernels run for this call.
-int pick_path(const imx_moe_config& c, const ExpertSet& s, int* path) {
+// Which expert kernels run for this call.  AUTO: tensor-memory GEMM tiles once
+// experts see enough rows to fill them, the decode kernels below that.
+int pick_path(const imx_moe_config& c, const ExpertSet& s, long n_rows, int* path) {
     int p = c.path;
-    if (p == IMX_PATH_AUTO) p = decode_mma_supported(s) ? IMX_PATH_DECODE : IMX_PATH_GENERIC;
-    if (p == IMX_PATH_PREFILL) p = decode_mma_supported(s) ? IMX_PATH_DECODE : IMX_PATH_GENERIC;
+    const bool many = n_rows >= 32L * s.num_experts;
+    if (p == IMX_PATH_AUTO) {
+        if (many && prefill_umma_supported(s)) p = IMX_PATH_PREFILL;
+        else p = decode_mma_supported(s) ? IMX_PATH_DECODE : IMX_PATH_GENERIC;
+    }
+    IMX_REQUIRE(p != IMX_PATH_PREFILL || prefill_umma_supported(s),
+                "the prefill path supports affine 4-bit, group 64/128, sizes that are multiples of 128");
     IMX_REQUIRE((p != IMX_PATH_DECODE && p != IMX_PATH_DECODE_REGS) || decode_mma_supported(s),
                 "the decode path supports affine 2/4/8-bit, group 64/128, sizes that are multiples of 128");
     *path = p;
@@ -179,6 +185,7 @@ int pick_path(const imx_moe_config& c, const ExpertSet& s, int* path) {
 }
 
 int run_experts(int path, const GroupedArgs& ga, cudaStream_t stream, cudaEvent_t mid = nullptr) {
+    if (path == IMX_PATH_PREFILL) return launch_prefill_umma(ga, stream, mid);
     if (path == IMX_PATH_DECODE && decode_tma_supported(ga.set)) return launch_decode_tma(ga, stream, mid);
     if (path == IMX_PATH_DECODE || path == IMX_PATH_DECODE_REGS) return launch_decode_mma(ga, stream, mid);
     return launch_generic_grouped(ga, stream, mid);
@@ -293,11 +300,11 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     ExpertSet set;
     IMX_TRY(make_expert_set(c, f, w->gate_up, w->down, c.num_experts, has_shared ? w : nullptr, &set));
     int path;
-    IMX_TRY(pick_path(c, set, &path));
+    IMX_TRY(pick_path(c, set, (long)n_tokens * c.top_k, &path));
 
     const int A = n_tokens * c.top_k;
     int order[16];
-    decode_block_order((path == IMX_PATH_DECODE || path == IMX_PATH_DECODE_REGS) ? f.bits : 0, order);
+    decode_block_order(path != IMX_PATH_GENERIC ? f.bits : 0, order);
     auto mark = [&](int i) -> cudaError_t { return ev ? cudaEventRecord(ev[i], stream) : cudaSuccess; };
     IMX_CHECK_CUDA(mark(0));
     IMX_TRY(launch_route(x, n_tokens, c.hidden, w->router_w, w->router_logit_bias, c.num_experts, c.top_k,
@@ -313,7 +320,7 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     ex.n_tokens = n_tokens;
     ex.units = ws.units;
     ex.n_units = ws.n_units;
-    ex.unit_rows = kUnitRows;
+    ex.unit_rows = path == IMX_PATH_PREFILL ? kPrefillUnitRows : kUnitRows;
     ex.sched = ws.sched;
     IMX_TRY(launch_sort(ws.topk_idx, A, c.num_experts, ws.counts, ws.offsets, ws.perm, ws.inv_perm,
                         ws.sort_scratch, ws.sort_scratch_bytes, &ex, stream));
@@ -475,13 +482,14 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
     ExpertSet set;
     IMX_TRY(make_expert_set(c, f, *gate_up, *down, num_experts, nullptr, &set));
     int path;
-    IMX_TRY(pick_path(c, set, &path));
-    IMX_TRY(launch_build_units(offsets, num_experts, kUnitRows, ws.units, ws.n_units, ws.sched, stream));
+    IMX_TRY(pick_path(c, set, (long)n_rows, &path));
+    IMX_TRY(launch_build_units(offsets, num_experts, path == IMX_PATH_PREFILL ? kPrefillUnitRows : kUnitRows, ws.units,
+                               ws.n_units, ws.sched, stream));
     GroupedArgs ga = {};
     ga.set = set;
     ga.in = (const __half*)x_f16;
     ga.row_index = row_index;
-    if (path == IMX_PATH_DECODE || path == IMX_PATH_DECODE_REGS) {
+    if (path != IMX_PATH_GENERIC) {
         // gather the rows once, in the block order the decode kernels read
         int o[16];
         decode_block_order(f.bits, o);

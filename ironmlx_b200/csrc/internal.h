@@ -100,6 +100,10 @@ bool decode_mma_supported(const ExpertSet& s);
 int launch_decode_mma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 bool decode_tma_supported(const ExpertSet& s);
 int launch_decode_tma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
+// Prefill path: tiles of kPrefillUnitRows sorted slots on tcgen05/TMEM.
+constexpr int kPrefillUnitRows = 128;
+bool prefill_umma_supported(const ExpertSet& s);
+int launch_prefill_umma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 int launch_generic_grouped(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 
 int launch_combine(const float* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,

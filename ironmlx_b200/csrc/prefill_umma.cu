@@ -1,0 +1,445 @@
+// Prefill-regime grouped expert products on the 5th-generation tensor cores:
+// tcgen05.mma (kind::f16, fp16 x fp16 -> fp32) with the accumulator in tensor
+// memory, for affine 4-bit weights (group 64/128).
+//
+//   first product   act[slot, :] = silu(x W_gate^T) * (x W_up^T)       (moe.rs:26-30)
+//   second product  out[slot, :] = row_scale[slot] * (act W_down^T)    (moe.rs:31, 155-161)
+//
+// Tile = 128 sorted slots of one expert (the M side, one TMEM lane per slot) x
+// 128 output columns (first product: 64 gate rows + the matching 64 up rows,
+// so SwiGLU happens in the epilogue; second product: 128 down rows), K in
+// steps of 64 (one 128-byte swizzle atom per row).
+//
+// One persistent CTA per SM, 16 warps, specialised:
+//   warp 0        issues the MMAs (one elected lane): waits for a filled stage,
+//                 4 x tcgen05.mma (K=16 each) per stage, tcgen05.commit to
+//                 release the stage, and after the last K step to publish the
+//                 accumulator (two accumulators in TMEM: epilogue of tile i
+//                 overlaps the MMAs of tile i+1)
+//   warp 1        allocates / frees tensor memory
+//   warps 4..7    epilogue: tcgen05.ld of their 32 TMEM lanes, SwiGLU or row
+//                 scaling in registers, stores
+//   warps 8..15   producers: activations by 16-byte cp.async straight into the
+//                 128B-swizzled K-major layout (rows gathered through the
+//                 dispatch permutation, zero-filled past the expert's last
+//                 slot); weights dequantized on the fly: 16 bytes of packed
+//                 codes -> 32 fp16 values (exact integer codes from the
+//                 mantissa trick, then one HFMA2 with the group's scale and
+//                 bias) -> four swizzled 16-byte shared stores
+// Stages are handed over with mbarriers (full: 8 producer-warp arrivals, empty:
+// one tcgen05.commit).  Every wait is bounded; on expiry the CTA records a
+// status, all roles leave their loops and tensor memory is freed.
+// No TMA multicast, no clusters.
+#include "decode_common.cuh"
+
+namespace imx {
+
+namespace {
+
+using namespace decode;
+
+constexpr int kThreads = 512;
+constexpr int kStages = 4;
+constexpr int kTileM = 128, kTileN = 128, kTileK = 64;
+constexpr int kABytes = kTileM * kTileK * 2;      // 16 KB
+constexpr int kBBytes = kTileN * kTileK * 2;      // 16 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kProducerWarps = 8;
+constexpr int kProducerThreads = kProducerWarps * 32;
+constexpr int kSpin = 1 << 22;
+constexpr uint32_t kTmemCols = 256;               // two 128-column fp32 accumulators
+
+struct Bars {                                     // shared-memory control block
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; false (and the abort flag set) when it gives up or someone else did.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (int spin = 0; spin < kSpin; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 1023) == 1023 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major, 128-byte swizzle: rows of 128 bytes, atoms of 8 rows (1024 bytes).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16: D fp32, A/B fp16 K-major, N = 128, M = 128
+constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(kIdesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// What a tile is made of.
+struct TileInfo {
+    int expert, slot0, rows, ntile, extra;
+    int K, n_out;           // reduction length, output rows of this expert's matrix
+};
+
+template <bool SWIGLU>
+__device__ __forceinline__ TileInfo tile_info(const GroupedArgs& a, int tile, int nt_r, int nt_x, int tiles_r) {
+    // tiles of the routed experts first (nt_r column tiles per unit), then the extra expert's
+    TileInfo t;
+    const int n_r = a.n_units[1];
+    int unit, nt;
+    if (tile < tiles_r) {
+        unit = tile / nt_r;
+        nt = nt_r;
+        t.ntile = tile - unit * nt_r;
+    } else {
+        const int l = tile - tiles_r;
+        unit = n_r + l / nt_x;
+        nt = nt_x;
+        t.ntile = l - (l / nt_x) * nt_x;
+    }
+    (void)nt;
+    const WorkUnit u = a.units[unit];
+    t.expert = u.expert;
+    t.slot0 = u.slot0;
+    t.rows = u.rows;
+    t.extra = u.expert >= a.set.num_experts;
+    t.K = SWIGLU ? a.set.n_in : (t.extra ? a.set.x_mid : a.set.n_mid);
+    t.n_out = SWIGLU ? (t.extra ? a.set.x_mid : a.set.n_mid) : a.set.n_in;
+    return t;
+}
+
+// Weight matrix and first row of the B tile's row `brow` (0..127).
+template <bool SWIGLU>
+__device__ __forceinline__ void b_row(const GroupedArgs& a, const TileInfo& t, int brow, QMat& m, int& row) {
+    const ExpertSet& S = a.set;
+    if (SWIGLU) {
+        const bool up = brow >= 64;
+        m = t.extra ? (up ? S.x_up : S.x_gate) : (up ? S.up : S.gate);
+        if (!t.extra) {
+            m.w += (size_t)t.expert * S.gu_stride_w;
+            m.scales += (size_t)t.expert * S.gu_stride_s;
+            m.biases += (size_t)t.expert * S.gu_stride_s;
+        }
+        row = t.ntile * 64 + (up ? brow - 64 : brow);
+    } else {
+        m = t.extra ? S.x_down : S.down;
+        if (!t.extra) {
+            m.w += (size_t)t.expert * S.dn_stride_w;
+            m.scales += (size_t)t.expert * S.dn_stride_s;
+            m.biases += (size_t)t.expert * S.dn_stride_s;
+        }
+        row = t.ntile * 128 + brow;
+    }
+}
+
+__device__ __forceinline__ __half2 bf16_to_half2(uint16_t b) {
+    return __float2half2_rn(__uint_as_float((uint32_t)b << 16));
+}
+
+template <bool SWIGLU, bool G128>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    Bars* bars = reinterpret_cast<Bars*>(base + kStages * kStageBytes);
+    const uint32_t sbase = smem_u32(base);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    volatile int* abort_flag = &bars->abort;
+
+    const int n_r = a.n_units[1], n_x = a.n_units[0] - n_r;
+    const int tiles_r = n_r * nt_r;
+    const int total = tiles_r + n_x * nt_x;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&bars->full[s]), kProducerWarps);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bars->acc_full[b]), 1);
+            mbar_init(smem_u32(&bars->acc_empty[b]), 4);
+        }
+        bars->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    if (warp == 0) {
+        // ── MMA issuer ──────────────────────────────────────────────────────
+        int n = 0, it = 0;
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
+            const TileInfo t = tile_info<SWIGLU>(a, tile, nt_r, nt_x, tiles_r);
+            const int buf = it & 1;
+            if (!mbar_wait(smem_u32(&bars->acc_empty[buf]), ((it >> 1) & 1) ^ 1, abort_flag)) break;
+            tc_fence_after();
+            const int ksteps = t.K / kTileK;
+            bool ok = true;
+            for (int ks = 0; ks < ksteps; ++ks, ++n) {
+                const int s = n % kStages;
+                if (!mbar_wait(smem_u32(&bars->full[s]), (n / kStages) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint64_t da = smem_desc(sbase + s * kStageBytes);
+                    const uint64_t db = smem_desc(sbase + s * kStageBytes + kABytes);
+#pragma unroll
+                    for (int kk = 0; kk < kTileK / 16; ++kk)
+                        umma_f16(tmem + buf * kTileN, da + 2 * kk, db + 2 * kk, (ks > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(smem_u32(&bars->empty[s]));                 // stage free once these MMAs retire
+                    if (ks == ksteps - 1) umma_commit(smem_u32(&bars->acc_full[buf]));
+                }
+                __syncwarp();
+            }
+            if (!ok) break;
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ── epilogue ────────────────────────────────────────────────────────
+        const int q = warp - 4;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
+            const TileInfo t = tile_info<SWIGLU>(a, tile, nt_r, nt_x, tiles_r);
+            const int buf = it & 1;
+            if (!mbar_wait(smem_u32(&bars->acc_full[buf]), (it >> 1) & 1, abort_flag)) break;
+            tc_fence_after();
+            const int row = q * 32 + lane;
+            const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + buf * kTileN;
+            const bool valid = row < t.rows;
+            const int slot = t.slot0 + row;
+            if (SWIGLU) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(taddr + h * 32, g);
+                    tmem_ld32(taddr + 64 + h * 32, u);
+                    if (h == 1) {                       // all of this warp's TMEM reads are done
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[buf]));
+                    }
+                    if (valid) {
+                        __half* dst = a.act + (size_t)slot * a.act_stride + t.ntile * 64 + h * 32;
+#pragma unroll
+                        for (int blk = 0; blk < 2; ++blk) {
+                            __half2 o[8];
+#pragma unroll
+                            for (int p = 0; p < 16; p += 2) {
+                                const int f0 = blk * 16 + Codec<4>::order(p), f1 = blk * 16 + Codec<4>::order(p + 1);
+                                const float v0 = silu_f(__uint_as_float(g[f0])) * __uint_as_float(u[f0]);
+                                const float v1 = silu_f(__uint_as_float(g[f1])) * __uint_as_float(u[f1]);
+                                o[p >> 1] = __halves2half2(f32_to_f16_sat(v0), f32_to_f16_sat(v1));
+                            }
+                            *reinterpret_cast<uint4*>(dst + blk * 16) = *reinterpret_cast<uint4*>(&o[0]);
+                            *reinterpret_cast<uint4*>(dst + blk * 16 + 8) = *reinterpret_cast<uint4*>(&o[4]);
+                        }
+                    }
+                }
+            } else {
+                const float sc = (valid && a.row_scale) ? a.row_scale[slot] : 1.f;
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    uint32_t d[32];
+                    tmem_ld32(taddr + h * 32, d);
+                    if (h == 3) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[buf]));
+                    }
+                    if (valid) {
+                        float* dst = a.out + (size_t)slot * a.set.n_in + t.ntile * 128 + h * 32;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            *reinterpret_cast<float4*>(dst + i) =
+                                make_float4(__uint_as_float(d[i]) * sc, __uint_as_float(d[i + 1]) * sc,
+                                            __uint_as_float(d[i + 2]) * sc, __uint_as_float(d[i + 3]) * sc);
+                    }
+                }
+            }
+        }
+    } else if (warp >= 8) {
+        // ── producers ───────────────────────────────────────────────────────
+        const int ptid = tid - 256;
+        const int brow = ptid >> 1, bhalf = ptid & 1;
+        int n = 0;
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+            const TileInfo t = tile_info<SWIGLU>(a, tile, nt_r, nt_x, tiles_r);
+            // activation chunks this thread copies every K step: 4 x (row, 16-byte chunk)
+            const __half* asrc[4];
+            uint32_t adst[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int cid = ptid + kProducerThreads * i;
+                const int row = cid >> 3, ch = cid & 7;
+                adst[i] = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((ch ^ (row & 7)) << 4));
+                asrc[i] = nullptr;
+                if (row < t.rows) {
+                    const int slot = t.slot0 + row;
+                    if (SWIGLU) {
+                        const int r = a.row_index ? a.row_index[slot] : slot;
+                        asrc[i] = a.in + (size_t)r * a.set.n_in + ch * 8;
+                    } else {
+                        asrc[i] = a.act + (size_t)slot * a.act_stride + ch * 8;
+                    }
+                }
+            }
+            QMat m;
+            int wrow_i;
+            b_row<SWIGLU>(a, t, brow, m, wrow_i);
+            const uint8_t* wrow = m.w + (size_t)wrow_i * (t.K / 2) + bhalf * 16;
+            const int groups = t.K / (G128 ? 128 : 64);
+            const uint16_t* srow = reinterpret_cast<const uint16_t*>(m.scales) + (size_t)wrow_i * groups;
+            const uint16_t* brow_p = reinterpret_cast<const uint16_t*>(m.biases) + (size_t)wrow_i * groups;
+            const uint32_t bdst = (uint32_t)(kABytes + (brow >> 3) * 1024 + (brow & 7) * 128);
+            const int ksteps = t.K / kTileK;
+            bool ok = true;
+            for (int ks = 0; ks < ksteps; ++ks, ++n) {
+                const int s = n % kStages;
+                // loads that do not need the stage: packed codes, scale, bias
+                const uint4 pk = __ldg(reinterpret_cast<const uint4*>(wrow + (size_t)ks * 32));
+                const int grp = G128 ? (ks >> 1) : ks;
+                const __half2 sc2 = bf16_to_half2(__ldg(srow + grp));
+                const __half2 bi2 = bf16_to_half2(__ldg(brow_p + grp));
+                if (!mbar_wait(smem_u32(&bars->empty[s]), ((n / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                const uint32_t stage = sbase + s * kStageBytes;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    cp_async16(stage + adst[i], asrc[i] ? (const void*)(asrc[i] + (size_t)ks * kTileK) : (const void*)a.in,
+                               asrc[i] ? 16u : 0u);
+                const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
+                const __half2 c1024 = __float2half2_rn(1024.f), c64 = __float2half2_rn(64.f);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    // eight codes of a word -> (0,4) (1,5) (2,6) (3,7): the order the activation rows use
+                    uint32_t r[4];
+                    const uint32_t v = words[j], v8 = v >> 8;
+                    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(r[0]) : "r"(v));
+                    asm("lop3.b32 %0, %1, 0x00f000f0, 0x54005400, 0xea;" : "=r"(r[1]) : "r"(v));
+                    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(r[2]) : "r"(v8));
+                    asm("lop3.b32 %0, %1, 0x00f000f0, 0x54005400, 0xea;" : "=r"(r[3]) : "r"(v8));
+                    __half2 o[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __half2 qh = __hsub2(*reinterpret_cast<__half2*>(&r[e]), (e & 1) ? c64 : c1024);   // exact code
+                        o[e] = __hfma2(qh, sc2, bi2);                                                       // scale*q + bias
+                    }
+                    const uint32_t chunk = (uint32_t)(bhalf * 4 + j) ^ (uint32_t)(brow & 7);
+                    const uint32_t dst = stage + bdst + (chunk << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(*reinterpret_cast<uint32_t*>(&o[0])),
+                                 "r"(*reinterpret_cast<uint32_t*>(&o[1])), "r"(*reinterpret_cast<uint32_t*>(&o[2])),
+                                 "r"(*reinterpret_cast<uint32_t*>(&o[3]))
+                                 : "memory");
+                }
+                cp_async_wait_all();
+                fence_async_proxy();                 // generic-proxy writes -> visible to the tensor-core reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->full[s]));
+            }
+            if (!ok) break;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+    if (tid == 0 && bars->abort && a.status != nullptr) atomicExch(a.status, 3);
+}
+
+}  // namespace
+
+bool prefill_umma_supported(const ExpertSet& s) {
+    const QFormat& f = s.fmt;
+    if (f.mode != IMX_MODE_AFFINE || f.bits != 4) return false;
+    if (f.group != 64 && f.group != 128) return false;
+    if (s.n_in % 128 || s.n_mid % 128) return false;
+    if (s.has_extra && s.x_mid % 128) return false;
+    return true;
+}
+
+int launch_prefill_umma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid) {
+    IMX_REQUIRE(prefill_umma_supported(a.set), "prefill path: format/shape not supported");
+    if (a.max_units == 0) return IMX_OK;
+    const ExpertSet& s = a.set;
+    const size_t smem = (size_t)kStages * kStageBytes + sizeof(Bars) + 1024;
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, v = 0;
+        IMX_CHECK_CUDA(cudaGetDevice(&dev));
+        IMX_CHECK_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        sms = v;
+    }
+    const bool g128 = s.fmt.group == 128;
+    const int x_mid = s.has_extra ? s.x_mid : s.n_mid;
+    auto k_gu = g128 ? prefill_umma_kernel<true, true> : prefill_umma_kernel<true, false>;
+    auto k_dn = g128 ? prefill_umma_kernel<false, true> : prefill_umma_kernel<false, false>;
+    k_gu<<<sms, kThreads, smem, stream>>>(a, s.n_mid / 64, x_mid / 64);
+    IMX_CHECK_CUDA(cudaGetLastError());
+    if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
+    k_dn<<<sms, kThreads, smem, stream>>>(a, s.n_in / 128, s.n_in / 128);
+    IMX_CHECK_CUDA(cudaGetLastError());
+    return IMX_OK;
+}
+
+}  // namespace imx

@@ -46,7 +46,7 @@ def compare(cfg, x, p, y, tr, fast=False):
     return err
 
 
-@pytest.mark.parametrize("path", ["generic", "decode", "decode_regs"])
+@pytest.mark.parametrize("path", ["generic", "decode", "decode_regs", "prefill"])
 @pytest.mark.parametrize("cfg", [TINY, SMALL, CONFIGS["c1"]], ids=lambda c: c.name)
 def test_block_affine4(cuda, cfg, path):
     x, p, _, y, tr = run(cfg, cuda, path)
@@ -94,7 +94,7 @@ def test_decode_path_other_widths(cuda, bits, group):
     MoEConfig("wide-shared", 12, 256, 8, 2, 128, 384, seed=17),
     MoEConfig("crowded", 100, 128, 2, 2, 128, 128, seed=18),      # 100 rows per expert: many units
 ], ids=lambda c: c.name)
-@pytest.mark.parametrize("path", ["generic", "decode", "decode_regs"])
+@pytest.mark.parametrize("path", ["generic", "decode", "decode_regs", "prefill"])
 def test_block_edge_shapes(cuda, cfg, path):
     x, p, _, y, tr = run(cfg, cuda, path)
     compare(cfg, x, p, y, tr)
@@ -154,6 +154,19 @@ def test_host_io_entry_point(cuda):
     moe.forward_host(xh, yh)
     yd = moe.forward_with_stream(xh.to(cuda))
     assert torch.equal(yh.to(cuda), yd)
+
+
+@pytest.mark.parametrize("group", [64, 128])
+def test_prefill_shape_reduced(cuda, group):
+    """The prefill layer shape (hidden 2048, intermediate 512, shared expert, top-4 of 16 experts) with
+    1024 tokens: 256 rows per expert on average, ragged tiles, the tensor-memory GEMM path by AUTO."""
+    cfg = MoEConfig(f"c3-small-g{group}", tokens=1024, hidden=2048, num_experts=16, top_k=4, intermediate=512,
+                    shared_intermediate=512, group_size=group, seed=1)
+    x, p, moe, y, tr = run(cfg, cuda)                 # AUTO must pick the prefill path here
+    err = compare(cfg, x, p, y, tr, fast=True)
+    _, _, _, yd, _ = run(cfg, cuda, "decode", x, p)
+    assert O.rel_l2(y, yd) < 1e-3
+    print(f"{cfg.name} rel-L2 {err:.3e}")
 
 
 def test_c2_reduced_experts(cuda):
