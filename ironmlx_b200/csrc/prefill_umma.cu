@@ -26,8 +26,8 @@
 //                 codes -> 32 fp16 values (exact integer codes from the
 //                 mantissa trick, then one HFMA2 with the group's scale and
 //                 bias) -> four swizzled 16-byte shared stores
-// Stages are handed over with mbarriers (full: 8 producer-warp arrivals, empty:
-// one tcgen05.commit).  Every wait is bounded; on expiry the CTA records a
+// Stages are handed over with mbarriers (full: the 4 warps of the producer group
+// that owns the stage, empty: one tcgen05.commit).  Every wait is bounded; on expiry the CTA records a
 // status, all roles leave their loops and tensor memory is freed.
 // No TMA multicast, no clusters.
 #include "decode_common.cuh"
@@ -202,7 +202,7 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(smem_u32(&bars->full[s]), kProducerWarps);
+            mbar_init(smem_u32(&bars->full[s]), kProducerWarps / 2);
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -315,17 +315,22 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
         }
     } else if (warp >= 8) {
         // ── producers ───────────────────────────────────────────────────────
-        const int ptid = tid - 256;
-        const int brow = ptid >> 1, bhalf = ptid & 1;
-        int n = 0;
+        // Two groups of four warps: group 0 fills the even K steps, group 1 the odd
+        // ones, so two stages are always being produced at once.  Inside a group a
+        // thread owns one weight row of the tile: 32 bytes of packed codes per K step
+        // (prefetched two of its own steps ahead), dequantized into eight 16-byte
+        // chunks; the group's 128 threads also issue the 1024 activation chunks.
+        const int grp_id = (warp - 8) >> 2;
+        const int gtid = tid - 256 - grp_id * 128;        // 0..127 = B row
+        const int brow = gtid;
+        int n_tile0 = 0;                                  // stage counter at the start of the tile
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
             const TileInfo t = tile_info<SWIGLU>(a, tile, nt_r, nt_x, tiles_r);
-            // activation chunks this thread copies every K step: 4 x (row, 16-byte chunk)
-            const __half* asrc[4];
-            uint32_t adst[4];
+            const __half* asrc[8];
+            uint32_t adst[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int cid = ptid + kProducerThreads * i;
+            for (int i = 0; i < 8; ++i) {
+                const int cid = gtid + 128 * i;
                 const int row = cid >> 3, ch = cid & 7;
                 adst[i] = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((ch ^ (row & 7)) << 4));
                 asrc[i] = nullptr;
@@ -342,30 +347,41 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
             QMat m;
             int wrow_i;
             b_row<SWIGLU>(a, t, brow, m, wrow_i);
-            const uint8_t* wrow = m.w + (size_t)wrow_i * (t.K / 2) + bhalf * 16;
+            const uint8_t* wrow = m.w + (size_t)wrow_i * (t.K / 2);
             const int groups = t.K / (G128 ? 128 : 64);
             const uint16_t* srow = reinterpret_cast<const uint16_t*>(m.scales) + (size_t)wrow_i * groups;
             const uint16_t* brow_p = reinterpret_cast<const uint16_t*>(m.biases) + (size_t)wrow_i * groups;
             const uint32_t bdst = (uint32_t)(kABytes + (brow >> 3) * 1024 + (brow & 7) * 128);
             const int ksteps = t.K / kTileK;
+            // register prefetch of this thread's next K step
+            uint4 pk0, pk1;
+            uint32_t sb;                                   // scale | bias << 16 (bf16 bits)
+            auto prefetch = [&](int ks) {
+                const uint4* p = reinterpret_cast<const uint4*>(wrow + (size_t)ks * 32);
+                pk0 = __ldg(p);
+                pk1 = __ldg(p + 1);
+                const int g = G128 ? (ks >> 1) : ks;
+                sb = (uint32_t)__ldg(srow + g) | ((uint32_t)__ldg(brow_p + g) << 16);
+            };
+            if (grp_id < ksteps) prefetch(grp_id);
             bool ok = true;
-            for (int ks = 0; ks < ksteps; ++ks, ++n) {
+            for (int ks = grp_id; ks < ksteps; ks += 2) {
+                const int n = n_tile0 + ks;
                 const int s = n % kStages;
-                // loads that do not need the stage: packed codes, scale, bias
-                const uint4 pk = __ldg(reinterpret_cast<const uint4*>(wrow + (size_t)ks * 32));
-                const int grp = G128 ? (ks >> 1) : ks;
-                const __half2 sc2 = bf16_to_half2(__ldg(srow + grp));
-                const __half2 bi2 = bf16_to_half2(__ldg(brow_p + grp));
+                const uint4 c0 = pk0, c1 = pk1;
+                const __half2 sc2 = bf16_to_half2((uint16_t)(sb & 0xffffu));
+                const __half2 bi2 = bf16_to_half2((uint16_t)(sb >> 16));
+                if (ks + 2 < ksteps) prefetch(ks + 2);
                 if (!mbar_wait(smem_u32(&bars->empty[s]), ((n / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 const uint32_t stage = sbase + s * kStageBytes;
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
+                for (int i = 0; i < 8; ++i)
                     cp_async16(stage + adst[i], asrc[i] ? (const void*)(asrc[i] + (size_t)ks * kTileK) : (const void*)a.in,
                                asrc[i] ? 16u : 0u);
-                const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
+                const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
                 const __half2 c1024 = __float2half2_rn(1024.f), c64 = __float2half2_rn(64.f);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < 8; ++j) {
                     // eight codes of a word -> (0,4) (1,5) (2,6) (3,7): the order the activation rows use
                     uint32_t r[4];
                     const uint32_t v = words[j], v8 = v >> 8;
@@ -379,8 +395,7 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
                         const __half2 qh = __hsub2(*reinterpret_cast<__half2*>(&r[e]), (e & 1) ? c64 : c1024);   // exact code
                         o[e] = __hfma2(qh, sc2, bi2);                                                       // scale*q + bias
                     }
-                    const uint32_t chunk = (uint32_t)(bhalf * 4 + j) ^ (uint32_t)(brow & 7);
-                    const uint32_t dst = stage + bdst + (chunk << 4);
+                    const uint32_t dst = stage + bdst + (((uint32_t)j ^ (uint32_t)(brow & 7)) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(*reinterpret_cast<uint32_t*>(&o[0])),
                                  "r"(*reinterpret_cast<uint32_t*>(&o[1])), "r"(*reinterpret_cast<uint32_t*>(&o[2])),
                                  "r"(*reinterpret_cast<uint32_t*>(&o[3]))
@@ -392,6 +407,7 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
                 if (lane == 0) mbar_arrive(smem_u32(&bars->full[s]));
             }
             if (!ok) break;
+            n_tile0 += ksteps;
         }
     }
 
