@@ -195,6 +195,165 @@ route_kernel(const __nv_bfloat16* __restrict__ x, int H, const __nv_bfloat16* __
     }
 }
 
+
+// ── prefill-size router: logits on the tensor cores ─────────────────────────
+// 32 tokens x all experts per CTA with mma.sync m16n8k16 (bf16 x bf16 -> fp32):
+// activations and router rows stream through shared memory in K chunks of 64
+// (16-byte cp.async, double buffered), the fp32 logits of the tile land in
+// shared memory and each warp finishes 8 tokens with the same warp
+// softmax/top-k as the decode-size kernel.
+constexpr int kRT = 32;            // tokens per CTA
+constexpr int kRK = 64;            // K chunk
+constexpr int kRPad = 72;          // bf16 per smem row (64 + 8: conflict-free fragment loads)
+constexpr int kRThreads = 128;
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT>   // n-tiles of 8 experts per warp: E = 32 * NT
+__global__ void __launch_bounds__(kRThreads)
+route_mma_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const __nv_bfloat16* __restrict__ Wr,
+                 const float* __restrict__ logit_bias, int k, int norm, const __nv_bfloat16* __restrict__ w_sg,
+                 int32_t* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ shared_gate,
+                 __half* __restrict__ x16, const Order16 order) {
+    constexpr int E = 32 * NT;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* s_x = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [2][kRT][kRPad]
+    __nv_bfloat16* s_w = s_x + 2 * kRT * kRPad;                                      // [2][E][kRPad]
+    float* s_logits = reinterpret_cast<float*>(smem_raw);                            // [kRT][E] (reuses the buffers)
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int tok0 = blockIdx.x * kRT;
+
+    auto load_chunk = [&](int buf, int kc) {
+        // activations: 32 rows x 8 chunks of 16 bytes
+        for (int c = tid; c < kRT * 8; c += kRThreads) {
+            const int r = c >> 3, ch = c & 7;
+            const int tok = tok0 + r;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(s_x + (buf * kRT + r) * kRPad + ch * 8);
+            const __nv_bfloat16* src = x + (size_t)(tok < n_tokens ? tok : 0) * H + kc * kRK + ch * 8;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(tok < n_tokens ? 16 : 0) : "memory");
+        }
+        for (int c = tid; c < E * 8; c += kRThreads) {
+            const int r = c >> 3, ch = c & 7;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(s_w + (buf * E + r) * kRPad + ch * 8);
+            const __nv_bfloat16* src = Wr + (size_t)r * H + kc * kRK + ch * 8;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, 16;" ::"r"(dst), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    float acc[2][NT][4];
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
+
+    const int nchunks = H / kRK;
+    load_chunk(0, 0);
+    for (int kc = 0; kc < nchunks; ++kc) {
+        const int buf = kc & 1;
+        if (kc + 1 < nchunks) {
+            load_chunk(buf ^ 1, kc + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const __nv_bfloat16* xs = s_x + buf * kRT * kRPad;
+        const __nv_bfloat16* ws = s_w + (buf * E + warp * (8 * NT)) * kRPad;
+#pragma unroll
+        for (int kk = 0; kk < kRK / 16; ++kk) {
+            uint32_t af[2][4];
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                const __nv_bfloat16* p = xs + (m * 16 + g) * kRPad + kk * 16 + 2 * t;
+                af[m][0] = *reinterpret_cast<const uint32_t*>(p);
+                af[m][1] = *reinterpret_cast<const uint32_t*>(p + 8 * kRPad);
+                af[m][2] = *reinterpret_cast<const uint32_t*>(p + 8);
+                af[m][3] = *reinterpret_cast<const uint32_t*>(p + 8 * kRPad + 8);
+            }
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const __nv_bfloat16* p = ws + (n * 8 + g) * kRPad + kk * 16 + 2 * t;
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(p);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(p + 8);
+                mma_bf16(acc[0][n], af[0][0], af[0][1], af[0][2], af[0][3], b0, b1);
+                mma_bf16(acc[1][n], af[1][0], af[1][1], af[1][2], af[1][3], b0, b1);
+            }
+        }
+        __syncthreads();
+    }
+    // logits (+ bias) of the tile into shared memory
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            const int e = warp * (8 * NT) + n * 8 + 2 * t;
+            const float b0 = logit_bias ? logit_bias[e] : 0.f, b1 = logit_bias ? logit_bias[e + 1] : 0.f;
+            s_logits[(m * 16 + g) * E + e] = acc[m][n][0] + b0;
+            s_logits[(m * 16 + g) * E + e + 1] = acc[m][n][1] + b1;
+            s_logits[(m * 16 + g + 8) * E + e] = acc[m][n][2] + b0;
+            s_logits[(m * 16 + g + 8) * E + e + 1] = acc[m][n][3] + b1;
+        }
+    __syncthreads();
+    // each warp finishes 8 tokens: softmax/top-k, shared gate, fp16 copy
+    for (int r = warp * 8; r < warp * 8 + 8; ++r) {
+        const int tok = tok0 + r;
+        if (tok >= n_tokens) break;
+        softmax_topk_warp<NT>(s_logits + r * E, E, k, norm, topk_idx + (size_t)tok * k, topk_w + (size_t)tok * k);
+        const __nv_bfloat16* xr = x + (size_t)tok * H;
+        if (w_sg != nullptr) {
+            float acc_g = 0.f;
+            for (int c = lane * 8; c < H; c += 256) {
+                const uint4 xv = __ldg(reinterpret_cast<const uint4*>(xr + c));
+                const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w_sg + c));
+                const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv);
+                const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 xf = __bfloat1622float2(xb[i]), wf = __bfloat1622float2(wb[i]);
+                    acc_g = fmaf(xf.x, wf.x, acc_g);
+                    acc_g = fmaf(xf.y, wf.y, acc_g);
+                }
+            }
+            acc_g = warp_sum(acc_g);
+            if (lane == 0) shared_gate[tok] = 1.0f / (1.0f + expf(-acc_g));
+        }
+        if (x16 != nullptr) {
+            __half2* dst = reinterpret_cast<__half2*>(x16 + (size_t)tok * H);
+            for (int i = lane; i < H / 2; i += 32) {
+                const int blk = (2 * i) & ~15, p = (2 * i) & 15;
+                const float a = __bfloat162float(xr[blk + order.o[p]]);
+                const float b = __bfloat162float(xr[blk + order.o[p + 1]]);
+                dst[i] = __halves2half2(f32_to_f16_sat(a), f32_to_f16_sat(b));
+            }
+        }
+    }
+}
+
+template <int NT>
+int launch_route_mma(const void* x, int n, int H, const void* Wr, const float* logit_bias, int k, int norm,
+                     const void* w_sg, int32_t* topk_idx, float* topk_w, float* shared_gate, void* x16,
+                     const Order16& order, cudaStream_t stream) {
+    constexpr int E = 32 * NT;
+    const size_t stage = (size_t)2 * (kRT + E) * kRPad * sizeof(__nv_bfloat16);
+    const size_t logits = (size_t)kRT * E * sizeof(float);
+    const size_t smem = stage > logits ? stage : logits;
+    IMX_CHECK_CUDA(cudaFuncSetAttribute(route_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    route_mma_kernel<NT><<<ceil_div(n, kRT), kRThreads, smem, stream>>>(
+        (const __nv_bfloat16*)x, n, H, (const __nv_bfloat16*)Wr, logit_bias, k, norm, (const __nv_bfloat16*)w_sg,
+        topk_idx, topk_w, shared_gate, (__half*)x16, order);
+    IMX_CHECK_CUDA(cudaGetLastError());
+    return IMX_OK;
+}
+
 }  // namespace
 
 int launch_route(const void* x, int n, int H, const void* Wr, const float* logit_bias, int E, int k,
@@ -207,6 +366,15 @@ int launch_route(const void* x, int n, int H, const void* Wr, const float* logit
     IMX_REQUIRE(k >= 1 && k <= E, "route: top_k (%d) must be in 1..num_experts (%d)", k, E);
     IMX_REQUIRE(w_sg == nullptr || shared_gate != nullptr, "route: shared gate weight without output");
     if (n == 0) return IMX_OK;
+    if (n >= 256 && H % kRK == 0 && E % 32 == 0 && E <= 256) {
+        switch (E / 32) {
+            case 1: return launch_route_mma<1>(x, n, H, Wr, logit_bias, k, norm, w_sg, topk_idx, topk_w, shared_gate, x16, order, stream);
+            case 2: return launch_route_mma<2>(x, n, H, Wr, logit_bias, k, norm, w_sg, topk_idx, topk_w, shared_gate, x16, order, stream);
+            case 4: return launch_route_mma<4>(x, n, H, Wr, logit_bias, k, norm, w_sg, topk_idx, topk_w, shared_gate, x16, order, stream);
+            case 8: return launch_route_mma<8>(x, n, H, Wr, logit_bias, k, norm, w_sg, topk_idx, topk_w, shared_gate, x16, order, stream);
+            default: break;
+        }
+    }
     // cluster size: enough CTAs to cover the GPU at small N, experts split evenly
     int cs = 1;
     while (cs < 8 && (long)n * cs < 296 && E / (cs * 2) >= 16) cs *= 2;
