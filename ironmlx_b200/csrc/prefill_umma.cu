@@ -39,7 +39,7 @@ namespace {
 using namespace decode;
 
 constexpr int kThreads = 512;
-constexpr int kStages = 4;
+constexpr int kStages = 6;
 constexpr int kTileM = 128, kTileN = 128, kTileK = 64;
 constexpr int kABytes = kTileM * kTileK * 2;      // 16 KB
 constexpr int kBBytes = kTileN * kTileK * 2;      // 16 KB
@@ -365,6 +365,7 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
             };
             if (grp_id < ksteps) prefetch(grp_id);
             bool ok = true;
+            int pending = -1;                              // stage filled but not yet published
             for (int ks = grp_id; ks < ksteps; ks += 2) {
                 const int n = n_tile0 + ks;
                 const int s = n % kStages;
@@ -378,6 +379,7 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
                 for (int i = 0; i < 8; ++i)
                     cp_async16(stage + adst[i], asrc[i] ? (const void*)(asrc[i] + (size_t)ks * kTileK) : (const void*)a.in,
                                asrc[i] ? 16u : 0u);
+                asm volatile("cp.async.commit_group;" ::: "memory");
                 const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
                 const __half2 c1024 = __float2half2_rn(1024.f), c64 = __float2half2_rn(64.f);
 #pragma unroll
@@ -401,10 +403,21 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
                                  "r"(*reinterpret_cast<uint32_t*>(&o[3]))
                                  : "memory");
                 }
+                // publish the PREVIOUS stage of this group: its activation copies had a whole
+                // step to land, so this wait does not expose the L2 latency
+                if (pending >= 0) {
+                    asm volatile("cp.async.wait_group 1;" ::: "memory");
+                    fence_async_proxy();             // generic-proxy writes -> visible to the tensor-core reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars->full[pending]));
+                }
+                pending = s;
+            }
+            if (pending >= 0) {
                 cp_async_wait_all();
-                fence_async_proxy();                 // generic-proxy writes -> visible to the tensor-core reads
+                fence_async_proxy();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bars->full[s]));
+                if (lane == 0) mbar_arrive(smem_u32(&bars->full[pending]));
             }
             if (!ok) break;
             n_tile0 += ksteps;
