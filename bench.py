@@ -337,9 +337,15 @@ def main():
         line["gpu_launches"] = runner.launches_per_step * args.steps
         line.update(runner.extra())
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without tearing the communicator down: destroying NCCL while captured CUDA graphs
+        # that contain its collectives are still alive can block.  Every rank is past its last
+        # collective here (barrier), nothing is in flight (synchronize).
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

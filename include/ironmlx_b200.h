@@ -213,6 +213,14 @@ IMX_API int imx_moe_combine_scaled(const float* rows, const float* row_scale, co
                            int n_tokens, int top_k, int hidden, const float* shared_rows, void* y,
                            void* stream);
 
+/* The routed part only, left in fp32 and not rounded: y_f32[t] = sum over the
+ * slots of token t whose inv_perm entry is >= 0 of row_scale[slot]*rows[slot]
+ * (row_scale may be NULL).  A rank that owns a block of the experts produces
+ * this partial sum for all tokens; the ranks' partials are added by a
+ * reduce-scatter before the shared expert is added and the result rounded. */
+IMX_API int imx_moe_combine_partial(const float* rows, const float* row_scale, const int32_t* inv_perm,
+                            int n_tokens, int top_k, int hidden, float* y_f32, void* stream);
+
 /* dst[j, :] = src[index[j], :], rows of row_bytes bytes (a multiple of 4): the
  * `take_axis` of moe.rs:124-127, used to pack the dispatch and return buffers
  * of the expert-parallel exchange. */

@@ -60,6 +60,7 @@ SIGNATURES = {
                              _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "imx_moe_combine": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "imx_moe_combine_scaled": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "imx_moe_combine_partial": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "imx_gather_rows": (_i, [_vp, _vp, _i, _sz, _vp, _vp]),
     "imx_dequantize": (_i, [C.POINTER(QTensor), _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "imx_quantized_matmul": (_i, [_vp, _i, C.POINTER(QTensor), _i, _i, _i, _i, _i, _i, _vp, _vp]),

@@ -529,6 +529,14 @@ int imx_moe_combine_scaled(const float* rows, const float* row_scale, const int3
     return launch_combine(rows, row_scale, inv_perm, n_tokens, top_k, hidden, shared_rows, y, (cudaStream_t)stream);
 }
 
+int imx_moe_combine_partial(const float* rows, const float* row_scale, const int32_t* inv_perm, int n_tokens,
+                            int top_k, int hidden, float* y_f32, void* stream) {
+    IMX_REQUIRE(n_tokens >= 0, "combine: negative token count");
+    if (n_tokens == 0) return IMX_OK;
+    IMX_REQUIRE(rows && inv_perm && y_f32, "combine_partial: rows, inv_perm and y_f32 are required");
+    return launch_combine(rows, row_scale, inv_perm, n_tokens, top_k, hidden, nullptr, y_f32, (cudaStream_t)stream, true);
+}
+
 int imx_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst, void* stream) {
     IMX_REQUIRE(n_rows >= 0, "gather_rows: negative row count");
     if (n_rows == 0) return IMX_OK;

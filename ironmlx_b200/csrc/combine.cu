@@ -16,10 +16,11 @@ constexpr int kCThreads = 128;
 constexpr int kCCols = kCThreads * 4;      // columns per CTA
 constexpr int kMaxK = 64;
 
+template <bool F32_OUT>
 __global__ void __launch_bounds__(kCThreads)
 combine_kernel(const float* __restrict__ rows, const float* __restrict__ row_scale,
                const int32_t* __restrict__ inv_perm, int k, int H, const float* __restrict__ shared_rows,
-               __nv_bfloat16* __restrict__ y) {
+               void* __restrict__ y_out) {
     __shared__ int s_slot[kMaxK];
     const int t = blockIdx.x;
     const int tid = threadIdx.x;
@@ -64,6 +65,11 @@ combine_kernel(const float* __restrict__ rows, const float* __restrict__ row_sca
         const float4 v = __ldg(reinterpret_cast<const float4*>(shared_rows + (size_t)t * H + c));
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
+    if (F32_OUT) {           // partial sums of expert parallelism: summed across ranks before the rounding
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(y_out) + (size_t)t * H + c) = acc;
+        return;
+    }
+    __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(y_out);
     __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
     __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
     uint2 o;
@@ -102,12 +108,13 @@ int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t
 }
 
 int launch_combine(const float* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,
-                   const float* shared_rows, void* y, cudaStream_t stream) {
+                   const float* shared_rows, void* y, cudaStream_t stream, bool f32_out) {
     IMX_REQUIRE(k >= 1 && k <= kMaxK, "combine: top_k (%d) must be in 1..%d", k, kMaxK);
     IMX_REQUIRE(H % 4 == 0, "combine: hidden (%d) must be a multiple of 4", H);
     if (n == 0) return IMX_OK;
     dim3 grid(n, ceil_div(H, kCCols));
-    combine_kernel<<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, (__nv_bfloat16*)y);
+    if (f32_out) combine_kernel<true><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y);
+    else combine_kernel<false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y);
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }

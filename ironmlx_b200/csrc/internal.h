@@ -107,7 +107,7 @@ int launch_prefill_umma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t m
 int launch_generic_grouped(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 
 int launch_combine(const float* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,
-                   const float* shared_rows, void* y, cudaStream_t stream);
+                   const float* shared_rows, void* y, cudaStream_t stream, bool f32_out = false);
 int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,
                        cudaStream_t stream);
 

@@ -23,6 +23,15 @@ Per step and rank (n local tokens, k experts per token):
      per token in ascending expert order, plus the local gated shared expert
      (replicated weights, computed on a side stream under the exchanges).
 
+Decode-size batches use a second schedule with no variable sizes and no host
+sync (`forward_gathered`): all-gather the few tokens, route them everywhere
+(the router is replicated), run the local experts on the assignments that fall
+into the local block (the others are dropped by the sort), form fp32 partial
+sums per token, reduce-scatter them back to the token owners, add the local
+shared-expert rows and round.  Cross-rank sums are added in the collective's
+order, not in ascending expert order; results stay within the block's
+tolerance.
+
 The stage kernels come from a `stages` object (the C ABI on CUDA tensors in
 production; the tests substitute a CPU implementation to run the bookkeeping
 on gloo ranks).
@@ -71,7 +80,8 @@ class CudaStages:
         a = ids.numel()
         i32 = dict(dtype=torch.int32, device=ids.device)
         counts, offsets = torch.empty(num_experts, **i32), torch.empty(num_experts + 1, **i32)
-        perm, inv = torch.empty(max(a, 1), **i32), torch.empty(max(a, 1), **i32)
+        # perm is zero-filled: when ids are dropped, its tail stays a valid (unused) index
+        perm, inv = torch.zeros(max(a, 1), **i32), torch.empty(max(a, 1), **i32)
         nb = C.c_size_t(0)
         check(lib().imx_moe_sort_scratch_bytes(a, num_experts, C.byref(nb)))
         scratch = self._buf("sort", nb.value)
@@ -103,6 +113,19 @@ class CudaStages:
                                     n_rows, n_rows, None if row_scale is None else row_scale.data_ptr(),
                                     out.data_ptr(), scratch.data_ptr(), scratch.numel(), ops.stream_ptr()))
         return out
+
+    def combine_partial(self, rows, row_scale, inv_perm, n, k, hidden):
+        y = torch.empty(n, hidden, dtype=torch.float32, device=rows.device)
+        check(lib().imx_moe_combine_partial(rows.data_ptr(), None if row_scale is None else row_scale.data_ptr(),
+                                            inv_perm.data_ptr(), n, k, hidden, y.data_ptr(), ops.stream_ptr()))
+        return y
+
+    def combine(self, rows, inv_perm, n, k, hidden, shared_rows):
+        y = torch.empty(n, hidden, dtype=torch.bfloat16, device=rows.device)
+        check(lib().imx_moe_combine(rows.data_ptr(), inv_perm.data_ptr(), n, k, hidden,
+                                    None if shared_rows is None else shared_rows.data_ptr(), y.data_ptr(),
+                                    ops.stream_ptr()))
+        return y
 
     def combine_scaled(self, rows, row_scale, inv_perm, n, k, hidden, shared_rows):
         y = torch.empty(n, hidden, dtype=torch.bfloat16, device=rows.device)
@@ -171,6 +194,8 @@ class ExpertParallelMoE:
         self.side_stream = (torch.cuda.Stream()
                             if torch.cuda.is_available() and getattr(weights.router_w, "is_cuda", False) else None)
         self.last = {}
+        self._off_cache = {}
+        self.gather_limit = 1024         # global tokens up to which the gathered schedule is used
 
     # -- collectives -----------------------------------------------------------
     def _a2a(self, send, out_rows: int, in_splits: List[int], out_splits: List[int]):
@@ -179,7 +204,77 @@ class ExpertParallelMoE:
                                group=self.group)
         return recv
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, mode: str = "auto") -> torch.Tensor:
+        """mode: "a2a" (dispatch/return all-to-all), "gathered" (all-gather + reduce-scatter),
+        "auto" (gathered while the global batch is at most `gather_limit` tokens)."""
+        if mode == "gathered" or (mode == "auto" and x.shape[0] * self.world <= self.gather_limit):
+            return self.forward_gathered(x)
+        return self.forward_a2a(x)
+
+    def _offsets_0n(self, n, dev):
+        """[0, n] on the device, made once per n (no host-to-device copy inside a step)."""
+        t = self._off_cache.get(n)
+        if t is None:
+            t = torch.tensor([0, n], dtype=torch.int32, device=dev)
+            self._off_cache[n] = t
+        return t
+
+    def _all_gather(self, x):
+        out = torch.empty((self.world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        if dist.get_backend(self.group) == "gloo":
+            parts = [torch.empty_like(x) for _ in range(self.world)]
+            dist.all_gather(parts, x, group=self.group)
+            return torch.cat(parts, 0)
+        dist.all_gather_into_tensor(out, x, group=self.group)
+        return out
+
+    def _reduce_scatter(self, partial, n):
+        if dist.get_backend(self.group) == "gloo":          # gloo has no reduce-scatter: all-reduce and slice
+            dist.all_reduce(partial, group=self.group)
+            return partial[self.rank * n:(self.rank + 1) * n].contiguous()
+        out = torch.empty((n,) + tuple(partial.shape[1:]), dtype=partial.dtype, device=partial.device)
+        dist.reduce_scatter_tensor(out, partial, group=self.group)
+        return out
+
+    def forward_gathered(self, x: torch.Tensor) -> torch.Tensor:
+        st, w = self.st, self.w
+        n = x.shape[0]
+        dev = x.device
+        xg = self._all_gather(x.contiguous())
+        n_all = xg.shape[0]
+        idx, tw, sg, x16 = st.route(xg, w.router_w, w.router_logit_bias, self.k, self.norm, w.shared_expert_gate_w)
+        shared_rows = None
+        if self.Is:
+            off = self._offsets_0n(n, dev)
+            own = slice(self.rank * n, (self.rank + 1) * n)
+            run = lambda: st.experts(self.cfg_shared, w.shared_gate_up, w.shared_down, 1, x16[own].contiguous(), None,
+                                     off, n, sg[own].contiguous(), key="shared")
+            if self.side_stream is not None:
+                self.side_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self.side_stream):
+                    shared_rows = run()
+            else:
+                shared_rows = run()
+        # ids outside the local block become out of range and are dropped by the sort (moe.rs:100)
+        ids_local = (idx.reshape(-1) - self.rank * self.E_loc).to(torch.int32)
+        counts, off2, perm, inv = st.sort(ids_local, self.E_loc)
+        a_all = n_all * self.k
+        tok = torch.div(perm, self.k, rounding_mode="floor").to(torch.int32)
+        out = st.experts(self.cfg_routed, w.gate_up, w.down, self.E_loc, x16, tok, off2, a_all, None)
+        w_sorted = st.gather_rows(tw.reshape(-1, 1), perm).reshape(-1)
+        partial = st.combine_partial(out, w_sorted, inv, n_all, self.k, self.H)
+        mine = self._reduce_scatter(partial, n)
+        if self.side_stream is not None and shared_rows is not None:
+            torch.cuda.current_stream().wait_stream(self.side_stream)
+        ident = torch.arange(n, dtype=torch.int32, device=dev)
+        y = st.combine(mine, ident, n, 1, self.H, shared_rows)
+        own_idx = idx[self.rank * n:(self.rank + 1) * n]
+        self.last = {"topk_idx": own_idx, "topk_w": tw[self.rank * n:(self.rank + 1) * n], "counts": counts,
+                     "n_recv": -1, "mode": "gathered",
+                     "a2a_bytes": (self.world - 1) * n * self.H * 2 + (self.world - 1) * n * self.H * 4}
+        return y
+
+    def forward_a2a(self, x: torch.Tensor) -> torch.Tensor:
         st, w = self.st, self.w
         n = x.shape[0]
         a = n * self.k
@@ -189,7 +284,7 @@ class ExpertParallelMoE:
         # shared expert: local tokens, replicated weights, off the critical path
         shared_rows = None
         if self.Is:
-            off = torch.tensor([0, n], dtype=torch.int32, device=dev)
+            off = self._offsets_0n(n, dev)
             if self.side_stream is not None:
                 self.side_stream.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(self.side_stream):
@@ -225,7 +320,7 @@ class ExpertParallelMoE:
         if self.side_stream is not None and shared_rows is not None:
             torch.cuda.current_stream().wait_stream(self.side_stream)
         y = st.combine_scaled(ret_rows, w_sorted, inv, n, self.k, self.H, shared_rows)
-        self.last = {"topk_idx": idx, "topk_w": tw, "perm": perm, "counts": counts, "n_recv": n_recv,
+        self.last = {"topk_idx": idx, "topk_w": tw, "perm": perm, "counts": counts, "n_recv": n_recv, "mode": "a2a",
                      "a2a_bytes": (sum(in_splits) - in_splits[self.rank]) * self.H * 2
                      + (sum(out_splits) - out_splits[self.rank]) * self.H * 4}
         return y
@@ -273,21 +368,48 @@ class BenchRunner:
         self.x = torch.from_numpy(x).to(device).to(torch.bfloat16)
         self.xh = self.x.cpu().pin_memory()
         self.yh = torch.empty_like(self.xh).pin_memory()
-        self.xd = torch.empty_like(self.x)
+        self.xd = self.x.clone()
+
+        # The gathered schedule has fixed shapes and no host sync: replay it as a CUDA graph
+        # (kernels, the two NCCL collectives and the side stream captured once).
+        self.graph = None
+        self.y = None
+        if self.moe.forward is not None and cfg.tokens * world <= self.moe.gather_limit:
+            try:
+                for _ in range(3):
+                    self.y = self.moe.forward(self.xd_static())
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self.y = self.moe.forward(self.xd)
+                self.graph = g
+            except Exception as e:            # capture not possible on this stack: run eagerly
+                self.graph = None
+                self.capture_error = repr(e)
+                torch.cuda.synchronize()
+
+    def xd_static(self):
+        self.xd.copy_(self.x)
+        return self.xd
 
     def step(self):
-        return self.moe.forward(self.x)
+        if self.graph is not None:
+            self.graph.replay()
+            return self.y
+        return self.moe.forward(self.xd)
 
     def step_host(self):
         self.xd.copy_(self.xh, non_blocking=True)
-        y = self.moe.forward(self.xd)
+        y = self.step()
         self.yh.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     def extra(self):
         return {"ep": {"experts_per_rank": self.moe.E_loc, "tokens_per_rank": self.cfg.tokens,
                        "a2a_bytes_per_rank_per_step": int(self.moe.last.get("a2a_bytes", 0)),
-                       "exchange": "NCCL all_to_all_single (dispatch fp16 rows, return fp32 rows) + count all-to-all"}}
+                       "schedule": self.moe.last.get("mode"), "cuda_graph": self.graph is not None,
+                       "exchange": "gathered: NCCL all-gather of tokens + reduce-scatter of fp32 partial rows; "
+                                   "a2a: NCCL all_to_all_single (fp16 rows out, fp32 rows back) + count all-to-all"}}
 
 
 def build_bench_runner(cfg, device, rank, world) -> BenchRunner:

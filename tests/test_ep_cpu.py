@@ -55,6 +55,20 @@ class NumpyStages:
             out *= row_scale.numpy()[:, None]
         return torch.from_numpy(out)
 
+    def combine_partial(self, rows, row_scale, inv_perm, n, k, hidden):
+        r, s, inv = rows.numpy(), row_scale.numpy(), inv_perm.numpy().reshape(n, k)
+        y = np.zeros((n, hidden), np.float64)
+        for t in range(n):
+            for slot in sorted(v for v in inv[t] if v >= 0):
+                y[t] += r[slot].astype(np.float64) * s[slot]
+        return torch.from_numpy(y.astype(np.float32))
+
+    def combine(self, rows, inv_perm, n, k, hidden, shared_rows):
+        y = rows.numpy()[inv_perm.numpy().reshape(n, k)].astype(np.float64).sum(1)
+        if shared_rows is not None:
+            y = y + shared_rows.numpy()
+        return torch.from_numpy(y.astype(np.float32)).to(torch.bfloat16)
+
     def combine_scaled(self, rows, row_scale, inv_perm, n, k, hidden, shared_rows):
         r, s, inv = rows.numpy(), row_scale.numpy(), inv_perm.numpy().reshape(n, k)
         y = np.zeros((n, hidden), np.float64)
@@ -86,10 +100,14 @@ def _worker(rank, world, port, out):
         x = Workload(CFG).activations(block=rank)            # every rank has its own tokens
         moe = ep.ExpertParallelMoE(NumpyStages(), local_weights(p, rank, world), CFG.num_experts, CFG.top_k, True,
                                    CFG.hidden, CFG.intermediate, CFG.shared_intermediate)
-        y = moe.forward(torch.from_numpy(x).to(torch.bfloat16)).float().numpy()
+        xt = torch.from_numpy(x).to(torch.bfloat16)
+        y = moe.forward(xt, mode="a2a").float().numpy()
         ref = O.moe_forward(x, p)
-        out[rank] = (O.rel_l2(y, ref.y), bool(np.array_equal(moe.last["perm"].numpy(), ref.perm)),
-                     int(moe.last["n_recv"]))
+        perm_ok = bool(np.array_equal(moe.last["perm"].numpy(), ref.perm))
+        n_recv = int(moe.last["n_recv"])
+        yg = moe.forward(xt, mode="gathered").float().numpy()
+        idx_ok = bool(np.array_equal(moe.last["topk_idx"].numpy(), ref.top_idx))
+        out[rank] = (max(O.rel_l2(y, ref.y), O.rel_l2(yg, ref.y)), perm_ok and idx_ok, n_recv)
     finally:
         dist.destroy_process_group()
 

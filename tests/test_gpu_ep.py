@@ -50,14 +50,18 @@ def _worker(rank, world, port, out):
         x = Workload(CFG).activations(block=rank)
         moe = ep.ExpertParallelMoE(ep.CudaStages(dev), local_from_params(p, dev, rank, world), CFG.num_experts,
                                    CFG.top_k, True, CFG.hidden, CFG.intermediate, CFG.shared_intermediate)
-        y = None
+        y = yg = None
         for _ in range(2):
-            y = moe.forward(t_bf16(x, dev))
+            y = moe.forward(t_bf16(x, dev), mode="a2a")
+        perm = moe.last["perm"].cpu().numpy()
+        for _ in range(2):
+            yg = moe.forward(t_bf16(x, dev), mode="gathered")
         torch.cuda.synchronize()
         single = moe_to_device(p, dev).forward_with_stream(t_bf16(x, dev))
         ref = O.moe_forward(x, p)
-        out[rank] = (O.rel_l2(bf16_to_np(y), ref.y), O.rel_l2(bf16_to_np(y), bf16_to_np(single)),
-                     bool(np.array_equal(moe.last["perm"].cpu().numpy(), ref.perm)))
+        out[rank] = (max(O.rel_l2(bf16_to_np(y), ref.y), O.rel_l2(bf16_to_np(yg), ref.y)),
+                     max(O.rel_l2(bf16_to_np(y), bf16_to_np(single)), O.rel_l2(bf16_to_np(yg), bf16_to_np(single))),
+                     bool(np.array_equal(perm, ref.perm)))
     finally:
         dist.destroy_process_group()
 
