@@ -54,6 +54,7 @@ struct ForwardWs {
     void* sort_scratch;
     size_t sort_scratch_bytes;
     __half* act;          // [A + N, act_stride]
+    __half* xs;           // [A + N, H] activations in slot order (prefill path)
     float* rows;          // [A + N, H]
     int max_units;
     int act_stride;
@@ -89,6 +90,7 @@ ForwardWs carve_forward(const imx_moe_config& c, int n, void* base) {
     w.sort_scratch = cv.take<uint8_t>(w.sort_scratch_bytes);
     w.act_stride = c.intermediate > c.shared_intermediate ? c.intermediate : c.shared_intermediate;
     w.act = cv.take<__half>((size_t)(A + ns) * w.act_stride);
+    w.xs = cv.take<__half>((size_t)(A + ns) * c.hidden);
     w.rows = cv.take<float>((size_t)(A + ns) * c.hidden);
     w.bytes = align_up(cv.off, 256);
     return w;
@@ -329,6 +331,8 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     ga.set = set;
     ga.in = ws.x16;
     ga.row_index = ws.tok_of_slot;
+    ga.xs = ws.xs;
+    ga.n_slots = A + (has_shared ? n_tokens : 0);
     ga.units = ws.units;
     ga.n_units = ws.n_units;
     ga.max_units = ws.max_units;
@@ -510,6 +514,8 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
     ga.row_scale = row_scale;
     ga.out = out;
     ga.status = nullptr;
+    ga.xs = nullptr;
+    ga.n_slots = n_rows;
     return run_experts(path, ga, stream);
 }
 

@@ -83,6 +83,8 @@ struct GroupedArgs {
     ExpertSet set;
     const __half* in;              // fp16 [.., n_in]
     const int32_t* row_index;      // per slot, row of `in` (nullptr: slot itself)
+    __half* xs;                    // [n_slots, n_in] scratch: `in` gathered into slot order (prefill path)
+    int n_slots;                   // slots covered by row_index / act / out
     const WorkUnit* units;
     const int32_t* n_units;
     int max_units;

@@ -19,17 +19,23 @@
 //   warp 1        allocates / frees tensor memory
 //   warps 4..7    epilogue: tcgen05.ld of their 32 TMEM lanes, SwiGLU or row
 //                 scaling in registers, stores
-//   warps 8..15   producers: activations by 16-byte cp.async straight into the
-//                 128B-swizzled K-major layout (rows gathered through the
-//                 dispatch permutation, zero-filled past the expert's last
-//                 slot); weights dequantized on the fly: 16 bytes of packed
-//                 codes -> 32 fp16 values (exact integer codes from the
-//                 mantissa trick, then one HFMA2 with the group's scale and
-//                 bias) -> four swizzled 16-byte shared stores
+//   warp 2        loads the activation tiles: one tiled TMA copy
+//                 (cp.async.bulk.tensor.2d, 128B swizzle) of 128 slots x 64
+//                 values per stage from the slot-ordered activation matrix
+//                 (first product: x gathered once into sorted-slot order;
+//                 second: the SwiGLU output, which is already slot-ordered);
+//                 rows past the tensor's end are zero-filled by the copy engine
+//   warps 8..15   weight producers, two groups of four warps on alternating K
+//                 steps; a thread owns one weight row of the tile: 32 bytes of
+//                 packed codes per K step -> 64 fp16 values (exact integer
+//                 codes from the mantissa trick, then one HFMA2 with the
+//                 group's scale and bias) -> eight swizzled 16-byte shared stores
 // Stages are handed over with mbarriers (full: the 4 warps of the producer group
-// that owns the stage, empty: one tcgen05.commit).  Every wait is bounded; on expiry the CTA records a
+// that owns the stage + the TMA transaction bytes, empty: one tcgen05.commit).  Every wait is bounded; on expiry the CTA records a
 // status, all roles leave their loops and tensor memory is freed.
-// No TMA multicast, no clusters.
+// Every copy is issued per CTA; the kernel uses no thread-block clusters.
+#include <cuda.h>
+
 #include "decode_common.cuh"
 
 namespace imx {
@@ -86,10 +92,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y)
+                 : "memory");
+}
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -188,7 +198,7 @@ __device__ __forceinline__ __half2 bf16_to_half2(uint16_t b) {
 
 template <bool SWIGLU, bool G128>
 __global__ void __launch_bounds__(kThreads, 1)
-prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
+prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const __grid_constant__ CUtensorMap amap) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     Bars* bars = reinterpret_cast<Bars*>(base + kStages * kStageBytes);
@@ -202,7 +212,7 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(smem_u32(&bars->full[s]), kProducerWarps / 2);
+            mbar_init(smem_u32(&bars->full[s]), kProducerWarps / 2 + 1);
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -245,6 +255,25 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
                         umma_f16(tmem + buf * kTileN, da + 2 * kk, db + 2 * kk, (ks > 0 || kk > 0) ? 1u : 0u);
                     umma_commit(smem_u32(&bars->empty[s]));                 // stage free once these MMAs retire
                     if (ks == ksteps - 1) umma_commit(smem_u32(&bars->acc_full[buf]));
+                }
+                __syncwarp();
+            }
+            if (!ok) break;
+        }
+    } else if (warp == 2) {
+        // ── activation loader (TMA) ─────────────────────────────────────────
+        int n = 0;
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+            const TileInfo t = tile_info<SWIGLU>(a, tile, nt_r, nt_x, tiles_r);
+            const int ksteps = t.K / kTileK;
+            bool ok = true;
+            for (int ks = 0; ks < ksteps; ++ks, ++n) {
+                const int s = n % kStages;
+                if (!mbar_wait(smem_u32(&bars->empty[s]), ((n / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                if (lane == 0) {
+                    const uint32_t bar = smem_u32(&bars->full[s]);
+                    mbar_expect_tx(bar, kABytes);
+                    tma_load_2d(sbase + s * kStageBytes, &amap, ks * kTileK, t.slot0, bar);
                 }
                 __syncwarp();
             }
@@ -318,32 +347,13 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
         // Two groups of four warps: group 0 fills the even K steps, group 1 the odd
         // ones, so two stages are always being produced at once.  Inside a group a
         // thread owns one weight row of the tile: 32 bytes of packed codes per K step
-        // (prefetched two of its own steps ahead), dequantized into eight 16-byte
-        // chunks; the group's 128 threads also issue the 1024 activation chunks.
+        // (prefetched one of its own steps ahead), dequantized into eight 16-byte chunks.
         const int grp_id = (warp - 8) >> 2;
         const int gtid = tid - 256 - grp_id * 128;        // 0..127 = B row
         const int brow = gtid;
         int n_tile0 = 0;                                  // stage counter at the start of the tile
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
             const TileInfo t = tile_info<SWIGLU>(a, tile, nt_r, nt_x, tiles_r);
-            const __half* asrc[8];
-            uint32_t adst[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int cid = gtid + 128 * i;
-                const int row = cid >> 3, ch = cid & 7;
-                adst[i] = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((ch ^ (row & 7)) << 4));
-                asrc[i] = nullptr;
-                if (row < t.rows) {
-                    const int slot = t.slot0 + row;
-                    if (SWIGLU) {
-                        const int r = a.row_index ? a.row_index[slot] : slot;
-                        asrc[i] = a.in + (size_t)r * a.set.n_in + ch * 8;
-                    } else {
-                        asrc[i] = a.act + (size_t)slot * a.act_stride + ch * 8;
-                    }
-                }
-            }
             QMat m;
             int wrow_i;
             b_row<SWIGLU>(a, t, brow, m, wrow_i);
@@ -365,7 +375,6 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
             };
             if (grp_id < ksteps) prefetch(grp_id);
             bool ok = true;
-            int pending = -1;                              // stage filled but not yet published
             for (int ks = grp_id; ks < ksteps; ks += 2) {
                 const int n = n_tile0 + ks;
                 const int s = n % kStages;
@@ -375,11 +384,6 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
                 if (ks + 2 < ksteps) prefetch(ks + 2);
                 if (!mbar_wait(smem_u32(&bars->empty[s]), ((n / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 const uint32_t stage = sbase + s * kStageBytes;
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    cp_async16(stage + adst[i], asrc[i] ? (const void*)(asrc[i] + (size_t)ks * kTileK) : (const void*)a.in,
-                               asrc[i] ? 16u : 0u);
-                asm volatile("cp.async.commit_group;" ::: "memory");
                 const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
                 const __half2 c1024 = __float2half2_rn(1024.f), c64 = __float2half2_rn(64.f);
 #pragma unroll
@@ -403,21 +407,9 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x) {
                                  "r"(*reinterpret_cast<uint32_t*>(&o[3]))
                                  : "memory");
                 }
-                // publish the PREVIOUS stage of this group: its activation copies had a whole
-                // step to land, so this wait does not expose the L2 latency
-                if (pending >= 0) {
-                    asm volatile("cp.async.wait_group 1;" ::: "memory");
-                    fence_async_proxy();             // generic-proxy writes -> visible to the tensor-core reads
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bars->full[pending]));
-                }
-                pending = s;
-            }
-            if (pending >= 0) {
-                cp_async_wait_all();
-                fence_async_proxy();
+                fence_async_proxy();                 // generic-proxy writes -> visible to the tensor-core reads
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bars->full[pending]));
+                if (lane == 0) mbar_arrive(smem_u32(&bars->full[s]));
             }
             if (!ok) break;
             n_tile0 += ksteps;
@@ -443,7 +435,40 @@ bool prefill_umma_supported(const ExpertSet& s) {
     return true;
 }
 
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// fp16 matrix [rows, cols] with `ld` elements between rows -> map whose box is one A tile
+// (64 columns x 128 rows, 128-byte swizzle); reads past the last row return zeros.
+int make_a_map(const void* base, size_t rows, size_t cols, size_t ld, CUtensorMap* out) {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        IMX_CHECK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        IMX_REQUIRE(p != nullptr && q == cudaDriverEntryPointSuccess, "prefill path: cuTensorMapEncodeTiled is not available");
+        fn = (EncodeTiledFn)p;
+    }
+    IMX_REQUIRE(((uintptr_t)base % 16) == 0 && (ld * 2) % 16 == 0, "prefill path: activation matrix must be 16-byte aligned");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)kTileM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    IMX_REQUIRE(r == CUDA_SUCCESS, "prefill path: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return IMX_OK;
+}
+
+}  // namespace
+
 int launch_prefill_umma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid) {
+    IMX_REQUIRE((a.row_index == nullptr || a.xs != nullptr) && a.n_slots > 0,
+                "prefill path: slot-ordered activation buffer missing");
     IMX_REQUIRE(prefill_umma_supported(a.set), "prefill path: format/shape not supported");
     if (a.max_units == 0) return IMX_OK;
     const ExpertSet& s = a.set;
@@ -463,10 +488,20 @@ int launch_prefill_umma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t m
     const int x_mid = s.has_extra ? s.x_mid : s.n_mid;
     auto k_gu = g128 ? prefill_umma_kernel<true, true> : prefill_umma_kernel<true, false>;
     auto k_dn = g128 ? prefill_umma_kernel<false, true> : prefill_umma_kernel<false, false>;
-    k_gu<<<sms, kThreads, smem, stream>>>(a, s.n_mid / 64, x_mid / 64);
+    // activations in sorted-slot order (the `take_axis` of moe.rs:124-127, once for all experts)
+    const __half* xsrc = a.in;                     // already slot-ordered when there is no row index
+    if (a.row_index != nullptr) {
+        IMX_TRY(launch_gather_rows(a.in, a.row_index, a.n_slots, (size_t)s.n_in * 2, a.xs, stream));
+        xsrc = a.xs;
+    }
+    CUtensorMap map_x, map_act;
+    IMX_TRY(make_a_map(xsrc, (size_t)a.n_slots, (size_t)s.n_in, (size_t)s.n_in, &map_x));
+    const int mid_max = s.n_mid > x_mid ? s.n_mid : x_mid;
+    IMX_TRY(make_a_map(a.act, (size_t)a.n_slots, (size_t)mid_max, (size_t)a.act_stride, &map_act));
+    k_gu<<<sms, kThreads, smem, stream>>>(a, s.n_mid / 64, x_mid / 64, map_x);
     IMX_CHECK_CUDA(cudaGetLastError());
     if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
-    k_dn<<<sms, kThreads, smem, stream>>>(a, s.n_in / 128, s.n_in / 128);
+    k_dn<<<sms, kThreads, smem, stream>>>(a, s.n_in / 128, s.n_in / 128, map_act);
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }
