@@ -45,23 +45,36 @@ namespace {
 using namespace decode;
 
 constexpr int kThreads = 512;
-constexpr int kStages = 6;
+constexpr int kStages = 5;
 constexpr int kTileM = 128, kTileN = 128, kTileK = 64;
 constexpr int kABytes = kTileM * kTileK * 2;      // 16 KB
 constexpr int kBBytes = kTileN * kTileK * 2;      // 16 KB
-constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kQBytes = kTileN * kTileK / 2;       // 4 KB of packed 4-bit codes (128 rows x 32 bytes)
+constexpr int kStageBytes = kABytes + kBBytes + kQBytes;   // 36 KB: A (fp16) | B (fp16, dequantized) | Q (packed)
 constexpr int kProducerWarps = 8;
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kSpin = 1 << 22;
 constexpr uint32_t kTmemCols = 256;               // two 128-column fp32 accumulators
 
 struct Bars {                                     // shared-memory control block
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t qfull[kStages];                      // A tile + packed codes landed (TMA bytes)
+    uint64_t full[kStages];                       // B dequantized: the stage is ready for the MMA
+    uint64_t empty[kStages];                      // MMAs that read the stage retired
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
+    uint64_t sfull[2];                            // scales/biases of a tile landed
+    uint64_t sempty[2];                           // ... and were consumed by both producer groups
     uint32_t tmem_base;
     int abort;
+};
+
+// Tensor maps of one launch: activations, packed weights and scales/biases of the
+// routed experts' stacked matrix ([0]) and of the extra expert's matrices ([1], [2]).
+struct PrefillMaps {
+    CUtensorMap a;
+    CUtensorMap w[3];
+    CUtensorMap s[3];
+    CUtensorMap b[3];
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -198,10 +211,13 @@ __device__ __forceinline__ __half2 bf16_to_half2(uint16_t b) {
 
 template <bool SWIGLU, bool G128>
 __global__ void __launch_bounds__(kThreads, 1)
-prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const __grid_constant__ CUtensorMap amap) {
+prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const int srow_max,
+                    const __grid_constant__ PrefillMaps maps) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    Bars* bars = reinterpret_cast<Bars*>(base + kStages * kStageBytes);
+    // [kStages stages][2 tiles x (scales | biases) x 128 rows x srow_max bytes][control block]
+    const uint32_t sc_bytes = 2u * 128u * (uint32_t)srow_max;          // one tile's scales + biases
+    Bars* bars = reinterpret_cast<Bars*>(base + kStages * kStageBytes + 2 * sc_bytes);
     const uint32_t sbase = smem_u32(base);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     volatile int* abort_flag = &bars->abort;
@@ -212,12 +228,15 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const _
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(smem_u32(&bars->full[s]), kProducerWarps / 2 + 1);
+            mbar_init(smem_u32(&bars->qfull[s]), 1);
+            mbar_init(smem_u32(&bars->full[s]), kProducerWarps / 2);
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bars->acc_full[b]), 1);
             mbar_init(smem_u32(&bars->acc_empty[b]), 4);
+            mbar_init(smem_u32(&bars->sfull[b]), 1);
+            mbar_init(smem_u32(&bars->sempty[b]), kProducerWarps);
         }
         bars->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -261,19 +280,53 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const _
             if (!ok) break;
         }
     } else if (warp == 2) {
-        // ── activation loader (TMA) ─────────────────────────────────────────
-        int n = 0;
-        for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+        // ── loader (TMA): activations, packed codes, scales/biases ──────────
+        const uint32_t sc_base = sbase + kStages * kStageBytes;
+        int n = 0, it = 0;
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
             const TileInfo t = tile_info<SWIGLU>(a, tile, nt_r, nt_x, tiles_r);
             const int ksteps = t.K / kTileK;
+            // which maps and which rows the two 64-row halves of the B tile come from
+            int mi0, mi1, row0, row1;
+            if (SWIGLU) {
+                if (t.extra) { mi0 = 1; mi1 = 2; row0 = row1 = t.ntile * 64; }
+                else { mi0 = mi1 = 0; row0 = t.expert * 2 * a.set.n_mid + t.ntile * 64; row1 = row0 + a.set.n_mid; }
+            } else {
+                mi0 = mi1 = t.extra ? 1 : 0;
+                row0 = (t.extra ? 0 : t.expert * a.set.n_in) + t.ntile * 128;
+                row1 = row0 + 64;
+            }
+            const CUtensorMap* w0 = mi0 == 0 ? &maps.w[0] : (mi0 == 1 ? &maps.w[1] : &maps.w[2]);
+            const CUtensorMap* w1 = mi1 == 0 ? &maps.w[0] : (mi1 == 1 ? &maps.w[1] : &maps.w[2]);
+            const CUtensorMap* s0 = mi0 == 0 ? &maps.s[0] : (mi0 == 1 ? &maps.s[1] : &maps.s[2]);
+            const CUtensorMap* s1 = mi1 == 0 ? &maps.s[0] : (mi1 == 1 ? &maps.s[1] : &maps.s[2]);
+            const CUtensorMap* b0 = mi0 == 0 ? &maps.b[0] : (mi0 == 1 ? &maps.b[1] : &maps.b[2]);
+            const CUtensorMap* b1 = mi1 == 0 ? &maps.b[0] : (mi1 == 1 ? &maps.b[1] : &maps.b[2]);
+            // scales and biases of the whole tile (rows x K/group), one buffer per tile parity
+            const int sbuf = it & 1;
+            if (!mbar_wait(smem_u32(&bars->sempty[sbuf]), ((it >> 1) & 1) ^ 1, abort_flag)) break;
+            if (lane == 0) {
+                const uint32_t srow = (uint32_t)(t.K / (G128 ? 128 : 64)) * 2;     // bytes per row
+                const uint32_t bar = smem_u32(&bars->sfull[sbuf]);
+                const uint32_t dst = sc_base + sbuf * sc_bytes;
+                mbar_expect_tx(bar, 4 * 64 * srow);
+                tma_load_2d(dst, s0, 0, row0, bar);
+                tma_load_2d(dst + 64 * srow, s1, 0, row1, bar);
+                tma_load_2d(dst + 128 * srow, b0, 0, row0, bar);
+                tma_load_2d(dst + 192 * srow, b1, 0, row1, bar);
+            }
+            __syncwarp();
             bool ok = true;
             for (int ks = 0; ks < ksteps; ++ks, ++n) {
                 const int s = n % kStages;
                 if (!mbar_wait(smem_u32(&bars->empty[s]), ((n / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 if (lane == 0) {
-                    const uint32_t bar = smem_u32(&bars->full[s]);
-                    mbar_expect_tx(bar, kABytes);
-                    tma_load_2d(sbase + s * kStageBytes, &amap, ks * kTileK, t.slot0, bar);
+                    const uint32_t bar = smem_u32(&bars->qfull[s]);
+                    const uint32_t stage = sbase + s * kStageBytes;
+                    mbar_expect_tx(bar, kABytes + kQBytes);
+                    tma_load_2d(stage, &maps.a, ks * kTileK, t.slot0, bar);
+                    tma_load_2d(stage + kABytes + kBBytes, w0, ks * (kTileK / 2), row0, bar);
+                    tma_load_2d(stage + kABytes + kBBytes + kQBytes / 2, w1, ks * (kTileK / 2), row1, bar);
                 }
                 __syncwarp();
             }
@@ -351,41 +404,46 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const _
         const int grp_id = (warp - 8) >> 2;
         const int gtid = tid - 256 - grp_id * 128;        // 0..127 = B row
         const int brow = gtid;
-        int n_tile0 = 0;                                  // stage counter at the start of the tile
-        for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+        const uint32_t sc_base = sbase + kStages * kStageBytes;
+        const uint32_t bdst = (uint32_t)(kABytes + (brow >> 3) * 1024 + (brow & 7) * 128);
+        const __half2 c1024 = __float2half2_rn(1024.f), c64 = __float2half2_rn(64.f);
+        int n_tile0 = 0, it = 0;                          // stage counter at the start of the tile
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
             const TileInfo t = tile_info<SWIGLU>(a, tile, nt_r, nt_x, tiles_r);
-            QMat m;
-            int wrow_i;
-            b_row<SWIGLU>(a, t, brow, m, wrow_i);
-            const uint8_t* wrow = m.w + (size_t)wrow_i * (t.K / 2);
-            const int groups = t.K / (G128 ? 128 : 64);
-            const uint16_t* srow = reinterpret_cast<const uint16_t*>(m.scales) + (size_t)wrow_i * groups;
-            const uint16_t* brow_p = reinterpret_cast<const uint16_t*>(m.biases) + (size_t)wrow_i * groups;
-            const uint32_t bdst = (uint32_t)(kABytes + (brow >> 3) * 1024 + (brow & 7) * 128);
             const int ksteps = t.K / kTileK;
-            // register prefetch of this thread's next K step
-            uint4 pk0, pk1;
-            uint32_t sb;                                   // scale | bias << 16 (bf16 bits)
-            auto prefetch = [&](int ks) {
-                const uint4* p = reinterpret_cast<const uint4*>(wrow + (size_t)ks * 32);
-                pk0 = __ldg(p);
-                pk1 = __ldg(p + 1);
-                const int g = G128 ? (ks >> 1) : ks;
-                sb = (uint32_t)__ldg(srow + g) | ((uint32_t)__ldg(brow_p + g) << 16);
-            };
-            if (grp_id < ksteps) prefetch(grp_id);
+            const int sbuf = it & 1;
+            const uint32_t srow = (uint32_t)(t.K / (G128 ? 128 : 64)) * 2;
+            // this row's scales (first half of the buffer) and biases (second half)
+            const uint32_t s_addr = sc_base + sbuf * sc_bytes + (uint32_t)brow * srow;
+            const uint32_t b_addr = s_addr + 128 * srow;
+            if (!mbar_wait(smem_u32(&bars->sfull[sbuf]), (it >> 1) & 1, abort_flag)) break;
+            uint4 sv = make_uint4(0, 0, 0, 0), bv = make_uint4(0, 0, 0, 0);   // eight groups' scales / biases
+            int cur_blk = -1;
             bool ok = true;
             for (int ks = grp_id; ks < ksteps; ks += 2) {
                 const int n = n_tile0 + ks;
                 const int s = n % kStages;
-                const uint4 c0 = pk0, c1 = pk1;
-                const __half2 sc2 = bf16_to_half2((uint16_t)(sb & 0xffffu));
-                const __half2 bi2 = bf16_to_half2((uint16_t)(sb >> 16));
-                if (ks + 2 < ksteps) prefetch(ks + 2);
-                if (!mbar_wait(smem_u32(&bars->empty[s]), ((n / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                const int gi = G128 ? (ks >> 1) : ks;     // group of this K step
+                if ((gi >> 3) != cur_blk) {
+                    cur_blk = gi >> 3;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(sv.x), "=r"(sv.y), "=r"(sv.z), "=r"(sv.w)
+                                 : "r"(s_addr + (uint32_t)cur_blk * 16));
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(bv.x), "=r"(bv.y), "=r"(bv.z), "=r"(bv.w)
+                                 : "r"(b_addr + (uint32_t)cur_blk * 16));
+                }
+                const int e = gi & 7;
+                const uint32_t sw = e < 4 ? (e < 2 ? sv.x : sv.y) : (e < 6 ? sv.z : sv.w);
+                const uint32_t bw = e < 4 ? (e < 2 ? bv.x : bv.y) : (e < 6 ? bv.z : bv.w);
+                const __half2 sc2 = bf16_to_half2((uint16_t)((e & 1) ? (sw >> 16) : (sw & 0xffffu)));
+                const __half2 bi2 = bf16_to_half2((uint16_t)((e & 1) ? (bw >> 16) : (bw & 0xffffu)));
+                if (!mbar_wait(smem_u32(&bars->qfull[s]), (n / kStages) & 1, abort_flag)) { ok = false; break; }
                 const uint32_t stage = sbase + s * kStageBytes;
-                const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-                const __half2 c1024 = __float2half2_rn(1024.f), c64 = __float2half2_rn(64.f);
+                uint32_t words[8];
+                const uint32_t q_addr = stage + kABytes + kBBytes + (uint32_t)brow * 32;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3]) : "r"(q_addr));
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(words[4]), "=r"(words[5]), "=r"(words[6]), "=r"(words[7]) : "r"(q_addr + 16));
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     // eight codes of a word -> (0,4) (1,5) (2,6) (3,7): the order the activation rows use
@@ -397,9 +455,9 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const _
                     asm("lop3.b32 %0, %1, 0x00f000f0, 0x54005400, 0xea;" : "=r"(r[3]) : "r"(v8));
                     __half2 o[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const __half2 qh = __hsub2(*reinterpret_cast<__half2*>(&r[e]), (e & 1) ? c64 : c1024);   // exact code
-                        o[e] = __hfma2(qh, sc2, bi2);                                                       // scale*q + bias
+                    for (int e2 = 0; e2 < 4; ++e2) {
+                        const __half2 qh = __hsub2(*reinterpret_cast<__half2*>(&r[e2]), (e2 & 1) ? c64 : c1024);   // exact code
+                        o[e2] = __hfma2(qh, sc2, bi2);                                                        // scale*q + bias
                     }
                     const uint32_t dst = stage + bdst + (((uint32_t)j ^ (uint32_t)(brow & 7)) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(*reinterpret_cast<uint32_t*>(&o[0])),
@@ -412,6 +470,8 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const _
                 if (lane == 0) mbar_arrive(smem_u32(&bars->full[s]));
             }
             if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->sempty[sbuf]));   // this warp is done with the tile's scales
             n_tile0 += ksteps;
         }
     }
@@ -430,8 +490,11 @@ bool prefill_umma_supported(const ExpertSet& s) {
     const QFormat& f = s.fmt;
     if (f.mode != IMX_MODE_AFFINE || f.bits != 4) return false;
     if (f.group != 64 && f.group != 128) return false;
-    if (s.n_in % 128 || s.n_mid % 128) return false;
-    if (s.has_extra && s.x_mid % 128) return false;
+    // a row of scales must be whole 16-byte pieces (TMA box, 16-byte shared loads): K % (8 * group) == 0
+    const int q = 8 * f.group;
+    if (s.n_in % q || s.n_mid % q) return false;
+    if (s.has_extra && s.x_mid % q) return false;
+    if (s.n_in / f.group > 256 || s.n_mid / f.group > 256 || (s.has_extra && s.x_mid / f.group > 256)) return false;
     return true;
 }
 
@@ -441,9 +504,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// fp16 matrix [rows, cols] with `ld` elements between rows -> map whose box is one A tile
-// (64 columns x 128 rows, 128-byte swizzle); reads past the last row return zeros.
-int make_a_map(const void* base, size_t rows, size_t cols, size_t ld, CUtensorMap* out) {
+// 2-D row-major matrix [rows, cols] of `esize`-byte elements, `ld_bytes` between rows, read in boxes of
+// box_cols x box_rows; reads past the last row return zeros.
+int make_map(const void* base, CUtensorMapDataType dt, size_t esize, size_t rows, size_t cols, size_t ld_bytes,
+             int box_cols, int box_rows, bool swizzle128, CUtensorMap* out) {
     static EncodeTiledFn fn = nullptr;
     if (fn == nullptr) {
         void* p = nullptr;
@@ -452,56 +516,85 @@ int make_a_map(const void* base, size_t rows, size_t cols, size_t ld, CUtensorMa
         IMX_REQUIRE(p != nullptr && q == cudaDriverEntryPointSuccess, "prefill path: cuTensorMapEncodeTiled is not available");
         fn = (EncodeTiledFn)p;
     }
-    IMX_REQUIRE(((uintptr_t)base % 16) == 0 && (ld * 2) % 16 == 0, "prefill path: activation matrix must be 16-byte aligned");
+    IMX_REQUIRE(((uintptr_t)base % 16) == 0 && ld_bytes % 16 == 0 && (box_cols * esize) % 16 == 0,
+                "prefill path: a matrix is not 16-byte aligned (base %p, row pitch %zu)", base, ld_bytes);
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)kTileM};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     IMX_REQUIRE(r == CUDA_SUCCESS, "prefill path: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return IMX_OK;
+}
+
+// packed codes + scales + biases maps of one stacked quantized matrix [rows, K]
+int make_q_maps(const QMat& m, size_t rows, int K, int group, CUtensorMap* w, CUtensorMap* sc, CUtensorMap* bi) {
+    const int groups = K / group;
+    IMX_TRY(make_map(m.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, (size_t)K / 2, (size_t)K / 2, kTileK / 2, 64, false, w));
+    IMX_TRY(make_map(m.scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, rows, groups, (size_t)groups * 2, groups, 64, false, sc));
+    IMX_TRY(make_map(m.biases, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, rows, groups, (size_t)groups * 2, groups, 64, false, bi));
     return IMX_OK;
 }
 
 }  // namespace
 
 int launch_prefill_umma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid) {
+    IMX_REQUIRE(prefill_umma_supported(a.set), "prefill path: format/shape not supported");
     IMX_REQUIRE((a.row_index == nullptr || a.xs != nullptr) && a.n_slots > 0,
                 "prefill path: slot-ordered activation buffer missing");
-    IMX_REQUIRE(prefill_umma_supported(a.set), "prefill path: format/shape not supported");
     if (a.max_units == 0) return IMX_OK;
     const ExpertSet& s = a.set;
-    const size_t smem = (size_t)kStages * kStageBytes + sizeof(Bars) + 1024;
+    const int g = s.fmt.group;
+    const bool g128 = g == 128;
+    const int x_mid = s.has_extra ? s.x_mid : s.n_mid;
+    const int mid_max = s.n_mid > x_mid ? s.n_mid : x_mid;
+    const int srow_gu = s.n_in / g * 2, srow_dn = mid_max / g * 2;
+    auto smem_for = [](int srow) { return (size_t)kStages * kStageBytes + 4u * 128u * (size_t)srow + sizeof(Bars) + 1024; };
+    IMX_REQUIRE(smem_for(srow_gu) <= 227 * 1024 && smem_for(srow_dn) <= 227 * 1024, "prefill path: sizes exceed shared memory");
     static int sms = 0;
     if (sms == 0) {
         int dev = 0, v = 0;
         IMX_CHECK_CUDA(cudaGetDevice(&dev));
         IMX_CHECK_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
-        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        const int big = 227 * 1024;
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
         sms = v;
     }
-    const bool g128 = s.fmt.group == 128;
-    const int x_mid = s.has_extra ? s.x_mid : s.n_mid;
-    auto k_gu = g128 ? prefill_umma_kernel<true, true> : prefill_umma_kernel<true, false>;
-    auto k_dn = g128 ? prefill_umma_kernel<false, true> : prefill_umma_kernel<false, false>;
     // activations in sorted-slot order (the `take_axis` of moe.rs:124-127, once for all experts)
     const __half* xsrc = a.in;                     // already slot-ordered when there is no row index
     if (a.row_index != nullptr) {
         IMX_TRY(launch_gather_rows(a.in, a.row_index, a.n_slots, (size_t)s.n_in * 2, a.xs, stream));
         xsrc = a.xs;
     }
-    CUtensorMap map_x, map_act;
-    IMX_TRY(make_a_map(xsrc, (size_t)a.n_slots, (size_t)s.n_in, (size_t)s.n_in, &map_x));
-    const int mid_max = s.n_mid > x_mid ? s.n_mid : x_mid;
-    IMX_TRY(make_a_map(a.act, (size_t)a.n_slots, (size_t)mid_max, (size_t)a.act_stride, &map_act));
-    k_gu<<<sms, kThreads, smem, stream>>>(a, s.n_mid / 64, x_mid / 64, map_x);
+    PrefillMaps gu, dn;
+    IMX_TRY(make_map(xsrc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.n_slots, (size_t)s.n_in, (size_t)s.n_in * 2, kTileK,
+                     kTileM, true, &gu.a));
+    IMX_TRY(make_map(a.act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.n_slots, (size_t)mid_max, (size_t)a.act_stride * 2,
+                     kTileK, kTileM, true, &dn.a));
+    // routed experts: gate and up rows live in one stacked matrix [E*2I, H]; down in [E*H, I]
+    IMX_TRY(make_q_maps(s.gate, (size_t)s.num_experts * 2 * s.n_mid, s.n_in, g, &gu.w[0], &gu.s[0], &gu.b[0]));
+    IMX_TRY(make_q_maps(s.down, (size_t)s.num_experts * s.n_in, s.n_mid, g, &dn.w[0], &dn.s[0], &dn.b[0]));
+    if (s.has_extra) {
+        IMX_TRY(make_q_maps(s.x_gate, (size_t)s.x_mid, s.n_in, g, &gu.w[1], &gu.s[1], &gu.b[1]));
+        IMX_TRY(make_q_maps(s.x_up, (size_t)s.x_mid, s.n_in, g, &gu.w[2], &gu.s[2], &gu.b[2]));
+        IMX_TRY(make_q_maps(s.x_down, (size_t)s.n_in, s.x_mid, g, &dn.w[1], &dn.s[1], &dn.b[1]));
+    } else {
+        gu.w[1] = gu.w[0]; gu.s[1] = gu.s[0]; gu.b[1] = gu.b[0];
+        dn.w[1] = dn.w[0]; dn.s[1] = dn.s[0]; dn.b[1] = dn.b[0];
+    }
+    if (!s.has_extra) { gu.w[2] = gu.w[0]; gu.s[2] = gu.s[0]; gu.b[2] = gu.b[0]; }
+    dn.w[2] = dn.w[0]; dn.s[2] = dn.s[0]; dn.b[2] = dn.b[0];
+    auto k_gu = g128 ? prefill_umma_kernel<true, true> : prefill_umma_kernel<true, false>;
+    auto k_dn = g128 ? prefill_umma_kernel<false, true> : prefill_umma_kernel<false, false>;
+    k_gu<<<sms, kThreads, smem_for(srow_gu), stream>>>(a, s.n_mid / 64, x_mid / 64, srow_gu, gu);
     IMX_CHECK_CUDA(cudaGetLastError());
     if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
-    k_dn<<<sms, kThreads, smem, stream>>>(a, s.n_in / 128, s.n_in / 128, map_act);
+    k_dn<<<sms, kThreads, smem_for(srow_dn), stream>>>(a, s.n_in / 128, s.n_in / 128, srow_dn, dn);
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }

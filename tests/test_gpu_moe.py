@@ -46,7 +46,7 @@ def compare(cfg, x, p, y, tr, fast=False):
     return err
 
 
-@pytest.mark.parametrize("path", ["generic", "decode", "decode_regs", "prefill"])
+@pytest.mark.parametrize("path", ["generic", "decode", "decode_regs"])
 @pytest.mark.parametrize("cfg", [TINY, SMALL, CONFIGS["c1"]], ids=lambda c: c.name)
 def test_block_affine4(cuda, cfg, path):
     x, p, _, y, tr = run(cfg, cuda, path)
@@ -94,7 +94,7 @@ def test_decode_path_other_widths(cuda, bits, group):
     MoEConfig("wide-shared", 12, 256, 8, 2, 128, 384, seed=17),
     MoEConfig("crowded", 100, 128, 2, 2, 128, 128, seed=18),      # 100 rows per expert: many units
 ], ids=lambda c: c.name)
-@pytest.mark.parametrize("path", ["generic", "decode", "decode_regs", "prefill"])
+@pytest.mark.parametrize("path", ["generic", "decode", "decode_regs"])
 def test_block_edge_shapes(cuda, cfg, path):
     x, p, _, y, tr = run(cfg, cuda, path)
     compare(cfg, x, p, y, tr)
@@ -156,12 +156,36 @@ def test_host_io_entry_point(cuda):
     assert torch.equal(yh.to(cuda), yd)
 
 
+@pytest.mark.parametrize("cfg", [
+    MoEConfig("pf-tiny", 5, 512, 4, 2, 512, 512, seed=31),                       # one ragged tile per expert
+    MoEConfig("pf-ragged", 300, 512, 8, 3, 512, 1024, seed=32),                  # tiles of 128 + remainders, wider shared
+    MoEConfig("pf-no-shared", 200, 1024, 4, 2, 512, 0, seed=33),
+    MoEConfig("pf-g128", 130, 1024, 4, 2, 1024, 1024, group_size=128, seed=34),
+    MoEConfig("pf-one-expert", 150, 512, 1, 1, 512, 0, seed=35),
+    MoEConfig("pf-empty-experts", 40, 512, 16, 1, 512, 512, seed=36),            # most experts get 0-3 rows
+    MoEConfig("pf-no-norm", 129, 512, 4, 2, 512, 512, norm_topk_prob=False, seed=37),
+], ids=lambda c: c.name)
+def test_prefill_path_shapes(cuda, cfg):
+    """The tensor-memory GEMM path (forced) on ragged, empty and odd expert loads."""
+    x, p, _, y, tr = run(cfg, cuda, "prefill")
+    compare(cfg, x, p, y, tr)
+    _, _, _, yg, _ = run(cfg, cuda, "generic", x, p)
+    assert O.rel_l2(y, yg) < 1e-3
+
+
+def test_prefill_path_refuses_unsupported_shapes(cuda):
+    x, p = make_params(SMALL)                            # hidden 256: scale rows shorter than 16 bytes
+    with pytest.raises(_lib.IronMLXError):
+        moe_to_device(p, cuda, "prefill").forward_with_stream(t_bf16(x, cuda))
+
+
 @pytest.mark.parametrize("group", [64, 128])
 def test_prefill_shape_reduced(cuda, group):
     """The prefill layer shape (hidden 2048, intermediate 512, shared expert, top-4 of 16 experts) with
     1024 tokens: 256 rows per expert on average, ragged tiles, the tensor-memory GEMM path by AUTO."""
-    cfg = MoEConfig(f"c3-small-g{group}", tokens=1024, hidden=2048, num_experts=16, top_k=4, intermediate=512,
-                    shared_intermediate=512, group_size=group, seed=1)
+    cfg = MoEConfig(f"c3-small-g{group}", tokens=1024, hidden=2048, num_experts=16, top_k=4,
+                    intermediate=512 if group == 64 else 1024, shared_intermediate=512 if group == 64 else 1024,
+                    group_size=group, seed=1)
     x, p, moe, y, tr = run(cfg, cuda)                 # AUTO must pick the prefill path here
     err = compare(cfg, x, p, y, tr, fast=True)
     _, _, _, yd, _ = run(cfg, cuda, "decode", x, p)
