@@ -59,6 +59,7 @@ extern "C" {
 #define IMX_PATH_PREFILL 2      /* grouped tcgen05/TMEM GEMM fed by TMA       */
 #define IMX_PATH_GENERIC 3      /* scalar dequant-GEMV, any format            */
 #define IMX_PATH_DECODE_REGS 4  /* decode kernel, register-pipelined variant  */
+#define IMX_PATH_DECODE_BULK 5  /* decode kernel fed by per-row bulk copies   */
 
 /* One quantized tensor: the (weight, scales, biases) triple of a
  * `QuantizedLinear` (mlx/src/nn/linear.rs:13-20).  biases is NULL for

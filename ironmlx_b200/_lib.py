@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libironmlx_
 
 OK, ERR_INVALID, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE = 0, 1, 2, 3, 4
 MODE = {"affine": 0, "mxfp8": 1, "nvfp4": 2}
-PATH = {"auto": 0, "decode": 1, "prefill": 2, "generic": 3, "decode_regs": 4}
+PATH = {"auto": 0, "decode": 1, "prefill": 2, "generic": 3, "decode_regs": 4, "decode_bulk": 5}
 MODE_DEFAULTS = {"affine": (64, 4), "mxfp8": (32, 8), "nvfp4": (16, 4)}
 
 

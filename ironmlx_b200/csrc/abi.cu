@@ -40,6 +40,7 @@ struct ForwardWs {
     int32_t* sched;       // [kSchedInts]
     int32_t* n_units;     // [4]: total, routed
     float* partials;      // [kFlagWarps][256] hand-off slots of the decode kernels
+    float* gsum;          // [A + N, max(H, act_stride) / 64] group sums of activation rows (decode kernels)
     int32_t* topk_idx;    // [A]
     float* topk_w;        // [A]
     float* shared_gate;   // [N]
@@ -92,6 +93,7 @@ ForwardWs carve_forward(const imx_moe_config& c, int n, void* base) {
     w.act = cv.take<__half>((size_t)(A + ns) * w.act_stride);
     w.xs = cv.take<__half>((size_t)(A + ns) * c.hidden);
     w.rows = cv.take<float>((size_t)(A + ns) * c.hidden);
+    w.gsum = cv.take<float>((size_t)(A + ns) * ((c.hidden > w.act_stride ? c.hidden : w.act_stride) / 64 + 1));
     w.bytes = align_up(cv.off, 256);
     return w;
 }
@@ -109,7 +111,7 @@ int check_config(const imx_moe_config* c, QFormat* f) {
                     c->shared_intermediate % 8 == 0,
                 "shared_intermediate (%d) must be a multiple of the group size and of 8", c->shared_intermediate);
     IMX_REQUIRE(c->hidden % f->group == 0, "hidden (%d) must be a multiple of the group size (%d)", c->hidden, f->group);
-    IMX_REQUIRE(c->path >= IMX_PATH_AUTO && c->path <= IMX_PATH_DECODE_REGS, "unknown path %d", c->path);
+    IMX_REQUIRE(c->path >= IMX_PATH_AUTO && c->path <= IMX_PATH_DECODE_BULK, "unknown path %d", c->path);
     return IMX_OK;
 }
 
@@ -180,7 +182,7 @@ int pick_path(const imx_moe_config& c, const ExpertSet& s, long n_rows, int* pat
     }
     IMX_REQUIRE(p != IMX_PATH_PREFILL || prefill_umma_supported(s),
                 "the prefill path supports affine 4-bit, group 64/128, sizes that are multiples of 128");
-    IMX_REQUIRE((p != IMX_PATH_DECODE && p != IMX_PATH_DECODE_REGS) || decode_mma_supported(s),
+    IMX_REQUIRE((p != IMX_PATH_DECODE && p != IMX_PATH_DECODE_REGS && p != IMX_PATH_DECODE_BULK) || decode_mma_supported(s),
                 "the decode path supports affine 2/4/8-bit, group 64/128, sizes that are multiples of 128");
     *path = p;
     return IMX_OK;
@@ -188,8 +190,11 @@ int pick_path(const imx_moe_config& c, const ExpertSet& s, long n_rows, int* pat
 
 int run_experts(int path, const GroupedArgs& ga, cudaStream_t stream, cudaEvent_t mid = nullptr) {
     if (path == IMX_PATH_PREFILL) return launch_prefill_umma(ga, stream, mid);
-    if (path == IMX_PATH_DECODE && decode_tma_supported(ga.set)) return launch_decode_tma(ga, stream, mid);
-    if (path == IMX_PATH_DECODE || path == IMX_PATH_DECODE_REGS) return launch_decode_mma(ga, stream, mid);
+    if (path == IMX_PATH_DECODE && decode_tmap_supported(ga.set)) return launch_decode_tmap(ga, stream, mid);
+    if ((path == IMX_PATH_DECODE || path == IMX_PATH_DECODE_BULK) && decode_tma_supported(ga.set))
+        return launch_decode_tma(ga, stream, mid);
+    if (path == IMX_PATH_DECODE || path == IMX_PATH_DECODE_REGS || path == IMX_PATH_DECODE_BULK)
+        return launch_decode_mma(ga, stream, mid);
     return launch_generic_grouped(ga, stream, mid);
 }
 
@@ -234,6 +239,7 @@ struct ExpertsWs {
     WorkUnit* units;
     __half* act;
     __half* xperm;       // activations re-ordered for the decode kernels
+    float* gsum;
     int max_units;
     size_t bytes;
 };
@@ -247,6 +253,7 @@ ExpertsWs carve_experts(const imx_moe_config& c, int n_rows, int n_src_rows, voi
     w.units = cv.take<WorkUnit>(w.max_units);
     w.act = cv.take<__half>((size_t)n_rows * c.intermediate);
     w.xperm = cv.take<__half>((size_t)n_src_rows * c.hidden);
+    w.gsum = cv.take<float>((size_t)n_rows * ((c.hidden > c.intermediate ? c.hidden : c.intermediate) / 64 + 1));
     w.bytes = align_up(cv.off, 256);
     return w;
 }
@@ -255,7 +262,10 @@ __global__ void permute_rows_kernel(const __half* __restrict__ src, const int32_
                                     int H, __half* __restrict__ dst, const Order16 order) {
     const int r = blockIdx.x;
     const __half* s = src + (size_t)(row_index ? row_index[r] : r) * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[(size_t)r * H + i] = s[(i & ~15) + order.o[i & 15]];
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const __half v = s[(i & ~15) + order.o[i & 15]];
+        dst[(size_t)r * H + i] = (i & 2) ? __float2half_rn(__half2float(v) * order.pair_scale_odd) : v;
+    }
 }
 }  // namespace
 
@@ -311,7 +321,8 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     IMX_CHECK_CUDA(mark(0));
     IMX_TRY(launch_route(x, n_tokens, c.hidden, w->router_w, w->router_logit_bias, c.num_experts, c.top_k,
                          c.norm_topk_prob, has_shared ? w->shared_expert_gate_w : nullptr, ws.topk_idx,
-                         ws.topk_w, ws.shared_gate, ws.x16, order, stream));
+                         ws.topk_w, ws.shared_gate, ws.x16, order, stream,
+                         path == IMX_PATH_DECODE && decode_tmap_supported(set) ? 0.0625f : 1.f));
     IMX_CHECK_CUDA(mark(1));
     SortExtras ex;
     ex.topk_w = ws.topk_w;
@@ -338,6 +349,7 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     ga.max_units = ws.max_units;
     ga.sched = ws.sched;
     ga.partials = ws.partials;
+    ga.gsum = ws.gsum;
     ga.act = ws.act;
     ga.act_stride = ws.act_stride;
     ga.row_scale = ws.w_of_slot;
@@ -499,6 +511,7 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
         decode_block_order(f.bits, o);
         Order16 order;
         for (int i = 0; i < 16; ++i) order.o[i] = (int8_t)o[i];
+        order.pair_scale_odd = path == IMX_PATH_DECODE && decode_tmap_supported(set) ? 0.0625f : 1.f;
         permute_rows_kernel<<<n_rows, 256, 0, stream>>>((const __half*)x_f16, row_index, c.hidden, ws.xperm, order);
         IMX_CHECK_CUDA(cudaGetLastError());
         ga.in = ws.xperm;
@@ -509,6 +522,7 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
     ga.max_units = ws.max_units;
     ga.sched = ws.sched;
     ga.partials = ws.partials;
+    ga.gsum = ws.gsum;
     ga.act = ws.act;
     ga.act_stride = c.intermediate;
     ga.row_scale = row_scale;

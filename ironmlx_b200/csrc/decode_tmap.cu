@@ -1,0 +1,595 @@
+// Decode-regime grouped expert products, tensor-map fed stream-K kernel
+// (affine 4-bit, group 64).  Same arithmetic as the other decode kernels
+// (exact integer codes on the fp16 tensor-core path, fp32 fold with scale and
+// bias per group); this variant is written for instruction count, because the
+// decode kernels are bound by issue slots, not by HBM:
+//
+//   * a stage (16 weight rows x 512 codes + their 8 scales and 8 biases per row)
+//     arrives with four tiled TMA copies issued by one lane: two 128-byte-wide
+//     swizzled boxes of packed codes and one 16-byte-wide box each of scales and
+//     biases, all completing on the stage's mbarrier.  Nothing about a stage
+//     passes through registers before it is used.
+//   * weight row r of a tile sits on MMA row r/2 + 8*(r&1): with the 128-byte
+//     swizzle the 8-byte fragment loads of a half-warp then cover all 32 banks.
+//   * a 4-bit code becomes an fp16 operand with one AND: left in the low mantissa
+//     bits of a half-word whose exponent field is zero it IS the subnormal
+//     q * 2^-24 (codes at bits [0,4)) or q * 2^-20 (codes at bits [4,8)).  No
+//     offset has to be added and none cancelled.  The two classes are levelled on
+//     the activation side: the fp16 activation rows these kernels read hold the
+//     values that meet a [4,8) code (odd reduction index) divided by 16 (exact
+//     down to 2^-10; Order16::pair_scale_odd).  The fold per group is
+//     acc += s*D + b*sum(x) with everything in units of 2^-24, and the epilogue
+//     multiplies by 2^24.
+//   * sum(x) * 2^-24 per (slot, group) comes from a table written by a small kernel
+//     before each product (group_sums_kernel), read two groups at a time.
+//   * activations and table entries of the next 128 codes are loaded while the
+//     current 128 are multiplied (register double buffer), across stage
+//     boundaries too.
+//
+// Work is cut as in decode_tma.cu: the (unit, tile pair, stage) sequence of the
+// launch is split into equal contiguous ranges, one per warp; a pair cut across
+// warps is finished by the warp that owns its first stage, the others hand their
+// fp32 partial sums over through the workspace.  Every wait is bounded.
+#include <cuda.h>
+
+#include <cstdio>
+#include <cstdlib>
+
+#include "decode_common.cuh"
+
+namespace imx {
+
+namespace {
+
+using namespace decode;
+
+constexpr int kStageCodes = 256;               // codes per row per stage, for both tiles of a pair
+constexpr int kWBytes = 2 * 16 * 128;          // packed codes of a stage: one box of 16 rows x 128 bytes per tile
+constexpr int kSBytes = 4 * 16 * 16;           // scales, biases of tile 0, then of tile 1: 16 rows x 8 groups x 2 bytes
+// shared memory of a CTA of `warps` warps with `stages` stages each: codes | scales+biases | barriers (+ slack to
+// align the base to 1024 bytes)
+constexpr size_t smem_bytes(int warps, int stages) {
+    return (size_t)warps * stages * (kWBytes + kSBytes + 8) + 1024;
+}
+constexpr int kSpinLimit = 1 << 20;
+constexpr int kFlagSpinLimit = 1 << 22;
+constexpr float kUnscale = 16777216.f;         // 2^24: the accumulators are in units of 2^-24
+
+// [0] the routed experts' stacked matrix, [1]/[2] the extra expert's matrix for tile 0 / tile 1 of a pair
+struct DecodeMaps {
+    CUtensorMap w[3];
+    CUtensorMap s[3];
+    CUtensorMap b[3];
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y)
+                 : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ void lds64(uint32_t addr, uint32_t (&v)[2]) {
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v[0]), "=r"(v[1]) : "r"(addr), "n"(OFF));
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+    return v;
+}
+// first MMA of a chain: accumulator input is zero
+// Loads that stay where they are written (ahead of the shared-memory loads and MMAs of the previous
+// 128 codes), so that their latency is covered.
+__device__ __forceinline__ uint4 ldg128_early(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void mma_f16_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    const float z = 0.f;
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(z));
+}
+
+// Unpack of a word of eight 4-bit codes into fp16 subnormals: the nibbles at bits
+// [0,4) of each half-word are q * 2^-24 as they stand, those at bits [4,8) are
+// q * 2^-20.  MMA m of a 16-code block takes r0 = codes (J, J+4) (reduction
+// indices 0..7 of the MMA) and r1 = codes (J+1, J+5) (indices 8..15).
+template <int M>
+__device__ __forceinline__ void frag2(const uint32_t (&w)[2], uint32_t& r0, uint32_t& r1) {
+    const uint32_t v = (M & 1) ? (w[M >> 1] >> 8) : w[M >> 1];
+    r0 = v & 0x000f000fu;
+    r1 = v & 0x00f000f0u;
+}
+
+// Position in the launch's stage sequence: routed units first, then the extra expert's units; within a
+// unit tile pair after tile pair, within a pair stage after stage.
+struct Cursor {
+    int unit, pair, st, extra;
+};
+
+// Sum of every group of 64 values of a row of fp16 activations, in units of 2^-24:
+// out[slot, j] = 2^-24 * sum(x[row(slot), 64 j .. 64 j + 63]), fixed order, fp32.  The rows are in the
+// expert kernels' layout: pairs 1 and 3 of every 8 stored values hold x / 16.
+__global__ void group_sums_kernel(const __half* __restrict__ in, const int32_t* __restrict__ row_index, int n_slots,
+                                  int groups, int ld, float* __restrict__ out) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_slots * groups) return;
+    const int slot = idx / groups, j = idx - slot * groups;
+    const int row = row_index ? row_index[slot] : slot;
+    const uint4* p = reinterpret_cast<const uint4*>(in + (size_t)row * ld + (size_t)j * 64);
+    float lo = 0.f, hi = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint4 v = __ldg(p + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+            if (e & 1) hi += f.x + f.y;
+            else lo += f.x + f.y;
+        }
+    }
+    out[idx] = (lo + 16.f * hi) * 5.9604644775390625e-8f;   // 2^-24
+}
+
+template <bool SWIGLU, int kWarps, int kStages>
+__global__ void __launch_bounds__(kWarps * 32, 1)
+decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const int st_r, const int st_x,
+                   const int flag_base, const int sum_groups, const __grid_constant__ DecodeMaps maps) {
+    constexpr int kSmemW = kWarps * kStages * kWBytes, kSmemS = kWarps * kStages * kSBytes;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);   // known to be warp-uniform
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t wbuf = sbase + (uint32_t)warp * (kStages * kWBytes);
+    const uint32_t sbuf = sbase + kSmemW + (uint32_t)warp * (kStages * kSBytes);
+    const uint32_t bars = sbase + kSmemW + kSmemS + (uint32_t)warp * (kStages * 8);
+
+    const int n_r = a.n_units[1];
+    const int stages_r = n_r * ppu_r * st_r;
+    const int total = stages_r + (a.n_units[0] - n_r) * ppu_x * st_x;
+
+    const int gw = blockIdx.x * kWarps + warp;
+    const int nw = gridDim.x * kWarps;
+    auto range_lo = [&](int w) { return (int)((long long)w * total / nw); };
+    const int sig_lo = range_lo(gw), sig_hi = range_lo(gw + 1);
+    if (sig_lo >= sig_hi) return;
+    int32_t* flags = a.sched + flag_base;
+    float* my_slot = a.partials + (size_t)gw * 256;
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) mbar_init(bars + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+
+    const ExpertSet& S = a.set;
+
+    // where the range starts (the only divisions of the kernel); both cursors advance stage by stage from here
+    Cursor start;
+    {
+        int local = sig_lo, ppu = ppu_r, st = st_r, unit0 = 0;
+        start.extra = 0;
+        if (sig_lo >= stages_r) {
+            local = sig_lo - stages_r;
+            ppu = ppu_x;
+            st = st_x;
+            unit0 = n_r;
+            start.extra = 1;
+        }
+        const int task = local / st;
+        start.st = local - task * st;
+        start.unit = unit0 + task / ppu;
+        start.pair = task - (task / ppu) * ppu;
+    }
+    // one stage forward; true when a new tile pair begins
+    auto advance = [&](Cursor& c) -> bool {
+        if (++c.st < (c.extra ? st_x : st_r)) return false;
+        c.st = 0;
+        if (++c.pair == (c.extra ? ppu_x : ppu_r)) {
+            c.pair = 0;
+            if (++c.unit == n_r) c.extra = 1;
+        }
+        return true;
+    };
+
+    // ── fetch side (warp-uniform; lane 0 issues the copies) ─────────────────
+    Cursor fc = start;
+    int f_sigma = sig_lo, f_unit = -1, f_expert = 0;
+    int f_map0 = 0, f_map1 = 0, f_row0 = 0, f_row1 = 0;
+    bool f_first = true;                // the first stage of the range fetches scales whatever its parity
+    auto fetch_rows = [&]() {           // rows of the pair's two tiles in their tensor maps
+        if (fc.unit != f_unit) {
+            f_unit = fc.unit;
+            f_expert = a.units[fc.unit].expert;
+        }
+        if (fc.extra) {
+            f_map0 = 1;
+            f_map1 = SWIGLU ? 2 : 1;
+            f_row0 = SWIGLU ? fc.pair * 16 : fc.pair * 32;
+            f_row1 = SWIGLU ? fc.pair * 16 : fc.pair * 32 + 16;
+        } else {
+            f_map0 = f_map1 = 0;
+            if (SWIGLU) {
+                f_row0 = f_expert * 2 * S.n_mid + fc.pair * 16;
+                f_row1 = f_row0 + S.n_mid;
+            } else {
+                f_row0 = f_expert * S.n_in + fc.pair * 32;
+                f_row1 = f_row0 + 16;
+            }
+        }
+    };
+    fetch_rows();
+    int n_fetch = 0, n_sfetch = 0;
+    auto issue = [&]() {
+        const bool with_scales = !(fc.st & 1) || f_first;   // a 16-byte row of scales serves two stages
+        if (lane == 0) {
+            const int slot = n_fetch % kStages;
+            const uint32_t bar = bars + 8 * slot;
+            const uint32_t wdst = wbuf + slot * kWBytes;
+            mbar_expect_tx(bar, with_scales ? kWBytes + kSBytes : kWBytes);
+            tma_load_2d(wdst, &maps.w[f_map0], fc.st * 128, f_row0, bar);
+            tma_load_2d(wdst + 2048, &maps.w[f_map1], fc.st * 128, f_row1, bar);
+            if (with_scales) {
+                const uint32_t sdst = sbuf + (n_sfetch % kStages) * kSBytes;
+                const int xs = (fc.st >> 1) * 8;
+                tma_load_2d(sdst, &maps.s[f_map0], xs, f_row0, bar);
+                tma_load_2d(sdst + 256, &maps.b[f_map0], xs, f_row0, bar);
+                tma_load_2d(sdst + 512, &maps.s[f_map1], xs, f_row1, bar);
+                tma_load_2d(sdst + 768, &maps.b[f_map1], xs, f_row1, bar);
+            }
+        }
+        if (with_scales) ++n_sfetch;
+        f_first = false;
+        ++n_fetch;
+        ++f_sigma;
+        if (advance(fc) && f_sigma < sig_hi) fetch_rows();
+    };
+
+    // ── compute side ────────────────────────────────────────────────────────
+    Cursor cc = start;
+    int c_sigma = sig_lo;
+    int c_st_lo = start.st;             // stage of its pair at which the current piece began
+    int c_unit = -1, c_rows = 0, c_slot0 = 0;
+    const __half* c_act = nullptr;      // this lane's activation row (slot g of the unit, clamped to a valid slot)
+    const float* c_sum_a = nullptr;     // group sums of slots 2t and 2t+1 (clamped likewise)
+    const float* c_sum_b = nullptr;
+    float c_rs0 = 1.f, c_rs1 = 1.f;     // output scale of slots 2t, 2t+1 (second product)
+    auto setup_unit = [&]() {
+        c_unit = cc.unit;
+        const WorkUnit u = a.units[cc.unit];
+        c_rows = u.rows;
+        c_slot0 = u.slot0;
+        const int last = u.rows - 1;
+        const int sl = u.slot0 + (g < last ? g : last);
+        const int sa = u.slot0 + (2 * t < last ? 2 * t : last), sb = u.slot0 + (2 * t + 1 < last ? 2 * t + 1 : last);
+        if (SWIGLU) {
+            const int row = a.row_index ? a.row_index[sl] : sl;
+            c_act = a.in + (size_t)row * S.n_in + t * 16;
+        } else {
+            c_act = a.act + (size_t)sl * a.act_stride + t * 16;
+            if (a.row_scale != nullptr) {
+                c_rs0 = a.row_scale[sa];
+                c_rs1 = a.row_scale[sb];
+            }
+        }
+        c_sum_a = a.gsum + (size_t)sa * sum_groups;
+        c_sum_b = a.gsum + (size_t)sb * sum_groups;
+    };
+    setup_unit();
+    float acc[2][4];
+#pragma unroll
+    for (int T = 0; T < 2; ++T)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[T][i] = 0.f;
+
+    // Finishes the piece that ends with the stage just computed (stage cc.st of pair cc.pair).
+    auto finish_piece = [&]() -> bool {
+        const int st_n = cc.extra ? st_x : st_r;
+        if (c_st_lo > 0) {
+            // not the owner: hand the partial sums to the warp that owns the pair's first stage
+#pragma unroll
+            for (int T = 0; T < 2; ++T)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) my_slot[(T * 4 + i) * 32 + lane] = acc[T][i];
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) *reinterpret_cast<volatile int32_t*>(flags + gw) = 1;
+        } else {
+            if (cc.st + 1 < st_n) {
+                // owner of a pair that was cut: add the partials of the following warps, in warp order
+                const int sigma_end = c_sigma - (cc.st + 1) + st_n;   // one past the pair's last stage
+                int covered = sig_hi;
+                for (int w = gw + 1; covered < sigma_end && w < nw; ++w) {
+                    if (range_lo(w + 1) == range_lo(w)) continue;   // a warp without work raises no flag
+                    int ok = 1;
+                    if (lane == 0) {
+                        int spin = 0;
+                        while (*reinterpret_cast<volatile int32_t*>(flags + w) == 0) {
+                            if (++spin > kFlagSpinLimit) {
+                                ok = 0;
+                                break;
+                            }
+                            __nanosleep(64);
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) {
+                        if (lane == 0 && a.status != nullptr) atomicExch(a.status, 2);
+                        return false;
+                    }
+                    __threadfence();
+                    const float* slot = a.partials + (size_t)w * 256;
+#pragma unroll
+                    for (int T = 0; T < 2; ++T)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            acc[T][i] += *reinterpret_cast<const volatile float*>(slot + (T * 4 + i) * 32 + lane);
+                    covered = range_lo(w + 1);
+                }
+            }
+            // accumulator i of a tile: weight row 2g + (i >> 1) of the tile, slot 2t + (i & 1) of the unit
+            if (SWIGLU) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int slot_l = 2 * t + (i & 1);
+                    const int row = cc.pair * 16 + 2 * g + (i >> 1);
+                    if (slot_l < c_rows) {
+                        float v = silu_f(acc[0][i] * kUnscale) * (acc[1][i] * kUnscale);
+                        if (row & 1) v *= 0.0625f;                                 // meets a [4,8) code in the second product
+                        const int col = (row & ~15) + permuted_pos<4>(row & 15);   // the order the second product reads
+                        a.act[(size_t)(c_slot0 + slot_l) * a.act_stride + col] = f32_to_f16_sat(v);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int T = 0; T < 2; ++T)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int slot_l = 2 * t + (i & 1);
+                        const int row = cc.pair * 32 + T * 16 + 2 * g + (i >> 1);
+                        if (slot_l < c_rows)
+                            a.out[(size_t)(c_slot0 + slot_l) * S.n_in + row] = acc[T][i] * (kUnscale * ((i & 1) ? c_rs1 : c_rs0));
+                    }
+            }
+        }
+#pragma unroll
+        for (int T = 0; T < 2; ++T)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[T][i] = 0.f;
+        return true;
+    };
+
+    // lane constants of the swizzled fragment loads: row 2g of a box, 8 bytes at (t & 1) * 8 of the
+    // 16-byte piece ((t >> 1) ^ row) -- the row below it is the same address ^ 144
+    const uint32_t lane_w = (uint32_t)g * 256u + (uint32_t)(t & 1) * 8u + ((((uint32_t)t >> 1) ^ ((2u * g) & 7u)) << 4);
+    const uint32_t lane_s = (uint32_t)g * 32u;
+
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s)
+        if (f_sigma < sig_hi) issue();
+    int n_comp = 0, n_scomp = 0;
+    uint32_t c_sslot = 0;                                // shared-memory offset of the scales the stage reads
+    bool c_first = true;
+    uint32_t bf[2][8];                                   // activations of 64 codes: [2 m + r] for MMA m
+    float sxa[4], sxb[4];                                // group sums of the stage's 4 groups: slot 2t, slot 2t+1
+    // activations of step j (64 codes) of the stage the compute cursor is at
+    auto load_step = [&](int buf, int j) {
+        const uint4* p = reinterpret_cast<const uint4*>(c_act + (size_t)cc.st * kStageCodes) + j * 8;
+        const uint4 v0 = ldg128_early(p), v1 = ldg128_early(p + 1);
+        bf[buf][0] = v0.x; bf[buf][1] = v0.y; bf[buf][2] = v0.z; bf[buf][3] = v0.w;
+        bf[buf][4] = v1.x; bf[buf][5] = v1.y; bf[buf][6] = v1.z; bf[buf][7] = v1.w;
+    };
+    auto load_sums = [&]() {
+        const uint4 va = ldg128_early(reinterpret_cast<const uint4*>(c_sum_a + cc.st * 4));
+        const uint4 vb = ldg128_early(reinterpret_cast<const uint4*>(c_sum_b + cc.st * 4));
+        sxa[0] = __uint_as_float(va.x); sxa[1] = __uint_as_float(va.y); sxa[2] = __uint_as_float(va.z); sxa[3] = __uint_as_float(va.w);
+        sxb[0] = __uint_as_float(vb.x); sxb[1] = __uint_as_float(vb.y); sxb[2] = __uint_as_float(vb.z); sxb[3] = __uint_as_float(vb.w);
+    };
+    load_sums();
+    load_step(0, 0);
+#pragma unroll 1
+    while (c_sigma < sig_hi) {
+        if (f_sigma < sig_hi) issue();                   // refills the slot that was consumed last
+
+        const int slot = n_comp % kStages;
+        if (!(cc.st & 1) || c_first) {
+            c_sslot = (uint32_t)(n_scomp % kStages) * kSBytes;
+            ++n_scomp;
+        }
+        c_first = false;
+        {
+            const uint32_t bar = bars + 8 * slot;
+            const uint32_t parity = (uint32_t)(n_comp / kStages) & 1u;
+            int spin = 0;
+            while (!mbar_try_wait(bar, parity)) {
+                if (++spin > kSpinLimit) {
+                    if (a.status != nullptr) atomicExch(a.status, 1);
+                    return;
+                }
+            }
+        }
+        const uint32_t wst = wbuf + (uint32_t)slot * kWBytes + lane_w;
+        const uint32_t sst = sbuf + c_sslot + lane_s + (uint32_t)(cc.st & 1) * 8u;   // groups 4 (st & 1) .. + 3 of the row
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int cur = j & 1;
+            if (j < 3) load_step(cur ^ 1, j + 1);
+            const uint32_t alo = wst ^ (uint32_t)(j * 32), ahi = alo ^ 144u;
+            const float xa = sxa[j], xb = sxb[j];
+#pragma unroll
+            for (int T = 0; T < 2; ++T) {
+                uint32_t wlo[2], whi[2];
+                if (T == 0) { lds64<0>(alo, wlo); lds64<0>(ahi, whi); }
+                else { lds64<2048>(alo, wlo); lds64<2048>(ahi, whi); }
+                // scales / biases of groups (j & ~1), (j | 1) for weight rows 2g (lo) and 2g+1 (hi) of tile T
+                uint32_t sc_lo, sc_hi, bi_lo, bi_hi;
+                if (T == 0 && j < 2) { sc_lo = lds32<0>(sst); sc_hi = lds32<16>(sst); bi_lo = lds32<256>(sst); bi_hi = lds32<272>(sst); }
+                if (T == 0 && j >= 2) { sc_lo = lds32<4>(sst); sc_hi = lds32<20>(sst); bi_lo = lds32<260>(sst); bi_hi = lds32<276>(sst); }
+                if (T == 1 && j < 2) { sc_lo = lds32<512>(sst); sc_hi = lds32<528>(sst); bi_lo = lds32<768>(sst); bi_hi = lds32<784>(sst); }
+                if (T == 1 && j >= 2) { sc_lo = lds32<516>(sst); sc_hi = lds32<532>(sst); bi_lo = lds32<772>(sst); bi_hi = lds32<788>(sst); }
+                const uint32_t* b = bf[cur];
+                float d[4];
+                uint32_t a0, a1, a2, a3;
+                frag2<0>(wlo, a0, a2); frag2<0>(whi, a1, a3);
+                mma_f16_z(d, a0, a1, a2, a3, b[0], b[1]);
+                frag2<1>(wlo, a0, a2); frag2<1>(whi, a1, a3);
+                mma_f16(d, a0, a1, a2, a3, b[2], b[3]);
+                frag2<2>(wlo, a0, a2); frag2<2>(whi, a1, a3);
+                mma_f16(d, a0, a1, a2, a3, b[4], b[5]);
+                frag2<3>(wlo, a0, a2); frag2<3>(whi, a1, a3);
+                mma_f16(d, a0, a1, a2, a3, b[6], b[7]);
+                // d = 2^-24 * sum of q * x over the group; fold with the group's scale and bias
+                const float s_lo = __uint_as_float((j & 1) ? (sc_lo & 0xffff0000u) : (sc_lo << 16));
+                const float s_hi = __uint_as_float((j & 1) ? (sc_hi & 0xffff0000u) : (sc_hi << 16));
+                const float b_lo = __uint_as_float((j & 1) ? (bi_lo & 0xffff0000u) : (bi_lo << 16));
+                const float b_hi = __uint_as_float((j & 1) ? (bi_hi & 0xffff0000u) : (bi_hi << 16));
+                acc[T][0] = fmaf(s_lo, d[0], fmaf(b_lo, xa, acc[T][0]));
+                acc[T][1] = fmaf(s_lo, d[1], fmaf(b_lo, xb, acc[T][1]));
+                acc[T][2] = fmaf(s_hi, d[2], fmaf(b_hi, xa, acc[T][2]));
+                acc[T][3] = fmaf(s_hi, d[3], fmaf(b_hi, xb, acc[T][3]));
+            }
+        }
+        __syncwarp();          // every lane is done reading this slot before it is refilled
+        ++n_comp;
+        ++c_sigma;
+        const bool pair_done = cc.st + 1 == (cc.extra ? st_x : st_r);
+        if (pair_done || c_sigma == sig_hi) {
+            if (!finish_piece()) return;
+            c_st_lo = 0;       // every piece after the first starts with its pair
+        }
+        advance(cc);
+        if (c_sigma < sig_hi) {
+            if (cc.unit != c_unit) setup_unit();
+            load_sums();       // first 64 codes and the sums of the next stage
+            load_step(0, 0);
+        }
+    }
+}
+
+}  // namespace
+
+bool decode_tmap_supported(const ExpertSet& s) {
+    const QFormat& f = s.fmt;
+    if (f.mode != IMX_MODE_AFFINE || f.bits != 4 || f.group != 64) return false;
+    if (s.n_in % 512 || s.n_mid % 512) return false;
+    if (s.has_extra && s.x_mid % 512) return false;
+    return true;
+}
+
+namespace {
+
+bool g_promote256 = false;
+
+int make_maps(const QMat& m, size_t rows, int K, CUtensorMap* w, CUtensorMap* sc, CUtensorMap* bi) {
+    const size_t groups = (size_t)K / 64;
+    IMX_TRY(make_tensor_map_2d(m.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, (size_t)K / 2, (size_t)K / 2, 128, 16, true, w,
+                               g_promote256));
+    IMX_TRY(make_tensor_map_2d(m.scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, rows, groups, groups * 2, 8, 16, false, sc));
+    IMX_TRY(make_tensor_map_2d(m.biases, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, rows, groups, groups * 2, 8, 16, false, bi));
+    return IMX_OK;
+}
+
+template <int kWarps, int kStages>
+int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn, int sms, cudaStream_t stream,
+                cudaEvent_t mid) {
+    const ExpertSet& s = a.set;
+    constexpr size_t smem = smem_bytes(kWarps, kStages);
+    static bool configured = false;
+    if (!configured) {
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(decode_tmap_kernel<true, kWarps, kStages>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(decode_tmap_kernel<false, kWarps, kStages>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    int grid = sms;
+    if (grid * kWarps > kFlagWarps) grid = kFlagWarps / kWarps;
+    const int x_mid = s.has_extra ? s.x_mid : s.n_mid;
+    const int mid_max = s.n_mid > x_mid ? s.n_mid : x_mid;
+    // first product: group sums of the input rows, then gate/up + SwiGLU
+    const int g_in = s.n_in / 64, g_mid = mid_max / 64;
+    {
+        const int n = a.n_slots * g_in;
+        group_sums_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a.in, a.row_index, a.n_slots, g_in, s.n_in, a.gsum);
+        IMX_CHECK_CUDA(cudaGetLastError());
+    }
+    decode_tmap_kernel<true, kWarps, kStages><<<grid, kWarps * 32, smem, stream>>>(
+        a, s.n_mid / 16, x_mid / 16, s.n_in / kStageCodes, s.n_in / kStageCodes, 8, g_in, gu);
+    IMX_CHECK_CUDA(cudaGetLastError());
+    if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
+    // second product: group sums of the SwiGLU rows, then down
+    {
+        const int n = a.n_slots * g_mid;
+        group_sums_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a.act, nullptr, a.n_slots, g_mid, a.act_stride, a.gsum);
+        IMX_CHECK_CUDA(cudaGetLastError());
+    }
+    decode_tmap_kernel<false, kWarps, kStages><<<grid, kWarps * 32, smem, stream>>>(
+        a, s.n_in / 32, s.n_in / 32, s.n_mid / kStageCodes, x_mid / kStageCodes, 8 + kFlagWarps, g_mid, dn);
+    IMX_CHECK_CUDA(cudaGetLastError());
+    return IMX_OK;
+}
+
+}  // namespace
+
+int launch_decode_tmap(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid) {
+    IMX_REQUIRE(decode_tmap_supported(a.set), "decode (tensor-map) path: format/shape not supported");
+    IMX_REQUIRE(a.partials != nullptr && a.sched != nullptr && a.gsum != nullptr && a.n_slots > 0,
+                "decode (tensor-map) path: workspace buffers missing");
+    if (a.max_units == 0) return IMX_OK;
+    const ExpertSet& s = a.set;
+    static int sms = 0, variant = 0;
+    if (sms == 0) {
+        int dev = 0, v = 0;
+        IMX_CHECK_CUDA(cudaGetDevice(&dev));
+        IMX_CHECK_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
+        const char* e = getenv("IMX_DECODE_VARIANT");
+        variant = e ? atoi(e) : 0;
+        g_promote256 = (variant & 4) != 0;
+        variant &= 3;
+        sms = v;
+    }
+    DecodeMaps gu, dn;
+    IMX_TRY(make_maps(s.gate, (size_t)s.num_experts * 2 * s.n_mid, s.n_in, &gu.w[0], &gu.s[0], &gu.b[0]));
+    IMX_TRY(make_maps(s.down, (size_t)s.num_experts * s.n_in, s.n_mid, &dn.w[0], &dn.s[0], &dn.b[0]));
+    if (s.has_extra) {
+        IMX_TRY(make_maps(s.x_gate, (size_t)s.x_mid, s.n_in, &gu.w[1], &gu.s[1], &gu.b[1]));
+        IMX_TRY(make_maps(s.x_up, (size_t)s.x_mid, s.n_in, &gu.w[2], &gu.s[2], &gu.b[2]));
+        IMX_TRY(make_maps(s.x_down, (size_t)s.n_in, s.x_mid, &dn.w[1], &dn.s[1], &dn.b[1]));
+    } else {
+        gu.w[1] = gu.w[2] = gu.w[0]; gu.s[1] = gu.s[2] = gu.s[0]; gu.b[1] = gu.b[2] = gu.b[0];
+        dn.w[1] = dn.w[0]; dn.s[1] = dn.s[0]; dn.b[1] = dn.b[0];
+    }
+    dn.w[2] = dn.w[1]; dn.s[2] = dn.s[1]; dn.b[2] = dn.b[1];
+    if (variant == 1) return launch_with<12, 3>(a, gu, dn, sms, stream, mid);
+    if (variant == 2) return launch_with<20, 2>(a, gu, dn, sms, stream, mid);
+    if (variant == 3) return launch_with<14, 3>(a, gu, dn, sms, stream, mid);
+    return launch_with<16, 2>(a, gu, dn, sms, stream, mid);
+}
+
+}  // namespace imx

@@ -1,5 +1,6 @@
 // Internal launcher declarations shared by the .cu files of the library.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -18,8 +19,11 @@ struct WorkUnit {
 };
 
 // Order of the 16 values inside each block of an fp16 activation row.
+// Stored pairs (2p, 2p+1) with odd p are multiplied by pair_scale_odd (1, or
+// 1/16 for the decode kernel that reads 4-bit codes as fp16 subnormals).
 struct Order16 {
     int8_t o[16];
+    float pair_scale_odd;
 };
 
 // Ints cleared by the sort stage before every pass of the expert kernels:
@@ -44,7 +48,7 @@ struct SortExtras {
 
 int launch_route(const void* x, int n, int H, const void* Wr, const float* logit_bias, int E, int k,
                  int norm, const void* w_sg, int32_t* topk_idx, float* topk_w, float* shared_gate,
-                 void* x16, const int* order16, cudaStream_t stream);
+                 void* x16, const int* order16, cudaStream_t stream, float pair_scale_odd = 1.f);
 
 // Order of the 16 values of each block of an fp16 activation row as the
 // expert kernels of a bit width read them (identity for the generic path).
@@ -90,6 +94,7 @@ struct GroupedArgs {
     int max_units;
     int32_t* sched;                // [kSchedInts]: counters, then the hand-off flags
     float* partials;               // [kFlagWarps][8][32] fp32 hand-off slots (decode kernels)
+    float* gsum;                   // [n_slots, max(n_in, act_stride) / 64] fp32 group sums (tensor-map decode kernel)
     __half* act;                   // fp16 [n_slots, act_stride]
     int act_stride;
     const float* row_scale;        // per slot or nullptr
@@ -100,12 +105,20 @@ struct GroupedArgs {
 bool decode_mma_supported(const ExpertSet& s);
 // `mid`, when given, is recorded between the first and the second product.
 int launch_decode_mma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
+// Tensor-map fed decode kernel (affine 4-bit, group 64); the preferred decode kernel where it applies.
+bool decode_tmap_supported(const ExpertSet& s);
+int launch_decode_tmap(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 bool decode_tma_supported(const ExpertSet& s);
 int launch_decode_tma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 // Prefill path: tiles of kPrefillUnitRows sorted slots on tcgen05/TMEM.
 constexpr int kPrefillUnitRows = 128;
 bool prefill_umma_supported(const ExpertSet& s);
 int launch_prefill_umma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
+// Tiled TMA descriptor of a 2-D row-major matrix [rows, cols] of `esize`-byte elements, `ld_bytes` between
+// rows, read in boxes of box_cols x box_rows (128-byte swizzle on request); reads past the end return zeros.
+int make_tensor_map_2d(const void* base, CUtensorMapDataType dt, size_t esize, size_t rows, size_t cols,
+                       size_t ld_bytes, int box_cols, int box_rows, bool swizzle128, CUtensorMap* out,
+                       bool promote256 = false);
 int launch_generic_grouped(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 
 int launch_combine(const float* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,

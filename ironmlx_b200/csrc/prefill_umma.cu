@@ -486,6 +486,35 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const i
 
 }  // namespace
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_tensor_map_2d(const void* base, CUtensorMapDataType dt, size_t esize, size_t rows, size_t cols,
+                       size_t ld_bytes, int box_cols, int box_rows, bool swizzle128, CUtensorMap* out,
+                       bool promote256) {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        IMX_CHECK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        IMX_REQUIRE(p != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available");
+        fn = (EncodeTiledFn)p;
+    }
+    IMX_REQUIRE(((uintptr_t)base % 16) == 0 && ld_bytes % 16 == 0 && (box_cols * esize) % 16 == 0,
+                "tensor map: a matrix is not 16-byte aligned (base %p, row pitch %zu)", base, ld_bytes);
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          promote256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    IMX_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return IMX_OK;
+}
+
 bool prefill_umma_supported(const ExpertSet& s) {
     const QFormat& f = s.fmt;
     if (f.mode != IMX_MODE_AFFINE || f.bits != 4) return false;
@@ -500,41 +529,12 @@ bool prefill_umma_supported(const ExpertSet& s) {
 
 namespace {
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// 2-D row-major matrix [rows, cols] of `esize`-byte elements, `ld_bytes` between rows, read in boxes of
-// box_cols x box_rows; reads past the last row return zeros.
-int make_map(const void* base, CUtensorMapDataType dt, size_t esize, size_t rows, size_t cols, size_t ld_bytes,
-             int box_cols, int box_rows, bool swizzle128, CUtensorMap* out) {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        IMX_CHECK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
-        IMX_REQUIRE(p != nullptr && q == cudaDriverEntryPointSuccess, "prefill path: cuTensorMapEncodeTiled is not available");
-        fn = (EncodeTiledFn)p;
-    }
-    IMX_REQUIRE(((uintptr_t)base % 16) == 0 && ld_bytes % 16 == 0 && (box_cols * esize) % 16 == 0,
-                "prefill path: a matrix is not 16-byte aligned (base %p, row pitch %zu)", base, ld_bytes);
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
-    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    IMX_REQUIRE(r == CUDA_SUCCESS, "prefill path: cuTensorMapEncodeTiled failed with %d", (int)r);
-    return IMX_OK;
-}
-
 // packed codes + scales + biases maps of one stacked quantized matrix [rows, K]
 int make_q_maps(const QMat& m, size_t rows, int K, int group, CUtensorMap* w, CUtensorMap* sc, CUtensorMap* bi) {
     const int groups = K / group;
-    IMX_TRY(make_map(m.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, (size_t)K / 2, (size_t)K / 2, kTileK / 2, 64, false, w));
-    IMX_TRY(make_map(m.scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, rows, groups, (size_t)groups * 2, groups, 64, false, sc));
-    IMX_TRY(make_map(m.biases, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, rows, groups, (size_t)groups * 2, groups, 64, false, bi));
+    IMX_TRY(make_tensor_map_2d(m.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, (size_t)K / 2, (size_t)K / 2, kTileK / 2, 64, false, w));
+    IMX_TRY(make_tensor_map_2d(m.scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, rows, groups, (size_t)groups * 2, groups, 64, false, sc));
+    IMX_TRY(make_tensor_map_2d(m.biases, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, rows, groups, (size_t)groups * 2, groups, 64, false, bi));
     return IMX_OK;
 }
 
@@ -572,9 +572,9 @@ int launch_prefill_umma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t m
         xsrc = a.xs;
     }
     PrefillMaps gu, dn;
-    IMX_TRY(make_map(xsrc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.n_slots, (size_t)s.n_in, (size_t)s.n_in * 2, kTileK,
+    IMX_TRY(make_tensor_map_2d(xsrc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.n_slots, (size_t)s.n_in, (size_t)s.n_in * 2, kTileK,
                      kTileM, true, &gu.a));
-    IMX_TRY(make_map(a.act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.n_slots, (size_t)mid_max, (size_t)a.act_stride * 2,
+    IMX_TRY(make_tensor_map_2d(a.act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.n_slots, (size_t)mid_max, (size_t)a.act_stride * 2,
                      kTileK, kTileM, true, &dn.a));
     // routed experts: gate and up rows live in one stacked matrix [E*2I, H]; down in [E*H, I]
     IMX_TRY(make_q_maps(s.gate, (size_t)s.num_experts * 2 * s.n_mid, s.n_in, g, &gu.w[0], &gu.s[0], &gu.b[0]));

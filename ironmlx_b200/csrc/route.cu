@@ -125,8 +125,9 @@ route_kernel(const __nv_bfloat16* __restrict__ x, int H, const __nv_bfloat16* __
         __half2* dst = reinterpret_cast<__half2*>(x16 + (size_t)token * H);
         for (int i = tid; i < H / 2; i += kRouteThreads) {
             const int blk = (2 * i) & ~15, p = (2 * i) & 15;
-            const float a = __bfloat162float(s_x[blk + order.o[p]]);
-            const float b = __bfloat162float(s_x[blk + order.o[p + 1]]);
+            const float sc = (i & 1) ? order.pair_scale_odd : 1.f;
+            const float a = __bfloat162float(s_x[blk + order.o[p]]) * sc;
+            const float b = __bfloat162float(s_x[blk + order.o[p + 1]]) * sc;
             dst[i] = __halves2half2(f32_to_f16_sat(a), f32_to_f16_sat(b));
         }
     }
@@ -330,8 +331,9 @@ route_mma_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const
             __half2* dst = reinterpret_cast<__half2*>(x16 + (size_t)tok * H);
             for (int i = lane; i < H / 2; i += 32) {
                 const int blk = (2 * i) & ~15, p = (2 * i) & 15;
-                const float a = __bfloat162float(xr[blk + order.o[p]]);
-                const float b = __bfloat162float(xr[blk + order.o[p + 1]]);
+                const float sc = (i & 1) ? order.pair_scale_odd : 1.f;
+                const float a = __bfloat162float(xr[blk + order.o[p]]) * sc;
+                const float b = __bfloat162float(xr[blk + order.o[p + 1]]) * sc;
                 dst[i] = __halves2half2(f32_to_f16_sat(a), f32_to_f16_sat(b));
             }
         }
@@ -358,10 +360,11 @@ int launch_route_mma(const void* x, int n, int H, const void* Wr, const float* l
 
 int launch_route(const void* x, int n, int H, const void* Wr, const float* logit_bias, int E, int k,
                  int norm, const void* w_sg, int32_t* topk_idx, float* topk_w, float* shared_gate,
-                 void* x16, const int* order16, cudaStream_t stream) {
+                 void* x16, const int* order16, cudaStream_t stream, float pair_scale_odd) {
     IMX_REQUIRE(n >= 0 && H > 0 && H % 16 == 0, "route: hidden (%d) must be a positive multiple of 16", H);
     Order16 order;
     for (int i = 0; i < 16; ++i) order.o[i] = (int8_t)(order16 ? order16[i] : i);
+    order.pair_scale_odd = pair_scale_odd;
     IMX_REQUIRE(E >= 1 && E <= 1024, "route: num_experts (%d) must be in 1..1024", E);
     IMX_REQUIRE(k >= 1 && k <= E, "route: top_k (%d) must be in 1..num_experts (%d)", k, E);
     IMX_REQUIRE(w_sg == nullptr || shared_gate != nullptr, "route: shared gate weight without output");

@@ -193,6 +193,32 @@ def test_prefill_shape_reduced(cuda, group):
     print(f"{cfg.name} rel-L2 {err:.3e}")
 
 
+@pytest.mark.parametrize("cfg", [
+    MoEConfig("tm-base", 24, 512, 8, 2, 512, 512, seed=31),
+    MoEConfig("tm-one-token", 1, 1024, 8, 2, 512, 512, seed=32),
+    MoEConfig("tm-no-shared", 33, 512, 16, 4, 1024, 0, seed=33),
+    MoEConfig("tm-wide-shared", 12, 1024, 8, 2, 512, 1536, seed=34),
+    MoEConfig("tm-crowded", 100, 512, 2, 2, 512, 512, seed=35),          # 100 rows per expert: many units
+    MoEConfig("tm-k-eq-e", 9, 512, 4, 4, 512, 1024, seed=36),
+], ids=lambda c: c.name)
+def test_decode_tensor_map_kernel(cuda, cfg):
+    """Shapes the tensor-map fed decode kernel takes (4-bit, group 64, sizes % 512 == 0): against the
+    checker, and against the bulk-copy decode kernel, which shares none of its data movement."""
+    x, p, _, y, tr = run(cfg, cuda, "decode")
+    compare(cfg, x, p, y, tr)
+    _, _, _, yb, _ = run(cfg, cuda, "decode_bulk", x, p)
+    assert O.rel_l2(y, yb) < 1e-3
+
+
+def test_decode_tensor_map_skew_and_empty(cuda):
+    cfg = MoEConfig("tm-skew", 64, 512, 32, 4, 512, 512, seed=37, zipf_s=1.2, zipf_hot_share=0.2)
+    x, p = make_params(cfg)
+    p.router_logit_bias[:8] = -30.0
+    x, p, _, y, tr = run(cfg, cuda, "decode", x, p)
+    assert (tr["counts"][:8] == 0).all()
+    compare(cfg, x, p, y, tr)
+
+
 def test_c2_reduced_experts(cuda):
     """The decode benchmark shape with 32 of the 256 experts (the checker
     finishes in seconds), 64 tokens, top-8, shared expert."""
