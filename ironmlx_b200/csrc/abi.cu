@@ -36,11 +36,14 @@ struct Carver {
 
 // Workspace of the fused forward.
 struct ForwardWs {
-    int32_t* status;      // [8]
+    int32_t* status;      // [16]: [0] device status word
     int32_t* sched;       // [kSchedInts]
     int32_t* n_units;     // [4]: total, routed
     float* partials;      // [kFlagWarps][256] hand-off slots of the decode kernels
-    float* gsum;          // [A + N, max(H, act_stride) / 64] group sums of activation rows (decode kernels)
+    float* gsum;          // [A + N, act_stride / 64] group sums of the SwiGLU rows (decode kernels)
+    float* gsum_x;        // [N, H / 64] group sums of the fp16 copy of x
+    float* route_partials;   // split-K router: [splits][32 ceil(N / 32)][E]
+    float* route_sg;         // split-K router: [splits][32 ceil(N / 32)]
     int32_t* topk_idx;    // [A]
     float* topk_w;        // [A]
     float* shared_gate;   // [N]
@@ -71,7 +74,7 @@ ForwardWs carve_forward(const imx_moe_config& c, int n, void* base) {
     const int A = n * c.top_k;
     const int ns = c.shared_intermediate > 0 ? n : 0;
     Carver cv(base);
-    w.status = cv.take<int32_t>(8);
+    w.status = cv.take<int32_t>(16);
     w.sched = cv.take<int32_t>(kSchedInts);
     w.n_units = cv.take<int32_t>(4);
     w.partials = cv.take<float>((size_t)kFlagWarps * 256);
@@ -93,7 +96,14 @@ ForwardWs carve_forward(const imx_moe_config& c, int n, void* base) {
     w.act = cv.take<__half>((size_t)(A + ns) * w.act_stride);
     w.xs = cv.take<__half>((size_t)(A + ns) * c.hidden);
     w.rows = cv.take<float>((size_t)(A + ns) * c.hidden);
-    w.gsum = cv.take<float>((size_t)(A + ns) * ((c.hidden > w.act_stride ? c.hidden : w.act_stride) / 64 + 1));
+    w.gsum = cv.take<float>((size_t)(A + ns) * (w.act_stride / 64 + 1));
+    w.gsum_x = cv.take<float>((size_t)n * (c.hidden / 64 + 1));
+    const int slice = route_slice(c.hidden);
+    if (n < kRouteSplitMaxTokens && slice > 0) {
+        const size_t splits = (size_t)c.hidden / slice, n_pad = (size_t)(n + 31) / 32 * 32;
+        w.route_partials = cv.take<float>(splits * n_pad * c.num_experts);
+        w.route_sg = cv.take<float>(splits * n_pad);
+    }
     w.bytes = align_up(cv.off, 256);
     return w;
 }
@@ -240,6 +250,7 @@ struct ExpertsWs {
     __half* act;
     __half* xperm;       // activations re-ordered for the decode kernels
     float* gsum;
+    float* gsum_x;
     int max_units;
     size_t bytes;
 };
@@ -253,7 +264,8 @@ ExpertsWs carve_experts(const imx_moe_config& c, int n_rows, int n_src_rows, voi
     w.units = cv.take<WorkUnit>(w.max_units);
     w.act = cv.take<__half>((size_t)n_rows * c.intermediate);
     w.xperm = cv.take<__half>((size_t)n_src_rows * c.hidden);
-    w.gsum = cv.take<float>((size_t)n_rows * ((c.hidden > c.intermediate ? c.hidden : c.intermediate) / 64 + 1));
+    w.gsum = cv.take<float>((size_t)n_rows * (c.intermediate / 64 + 1));
+    w.gsum_x = cv.take<float>((size_t)n_src_rows * (c.hidden / 64 + 1));
     w.bytes = align_up(cv.off, 256);
     return w;
 }
@@ -318,11 +330,14 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     int order[16];
     decode_block_order(path != IMX_PATH_GENERIC ? f.bits : 0, order);
     auto mark = [&](int i) -> cudaError_t { return ev ? cudaEventRecord(ev[i], stream) : cudaSuccess; };
+    const bool tmap_decode = path == IMX_PATH_DECODE && decode_tmap_supported(set);
+    RouteScratch rscratch = {ws.route_partials, ws.route_sg, tmap_decode ? ws.gsum_x : nullptr};
+    bool sums_done = false;
     IMX_CHECK_CUDA(mark(0));
     IMX_TRY(launch_route(x, n_tokens, c.hidden, w->router_w, w->router_logit_bias, c.num_experts, c.top_k,
                          c.norm_topk_prob, has_shared ? w->shared_expert_gate_w : nullptr, ws.topk_idx,
                          ws.topk_w, ws.shared_gate, ws.x16, order, stream,
-                         path == IMX_PATH_DECODE && decode_tmap_supported(set) ? 0.0625f : 1.f));
+                         tmap_decode ? 0.0625f : 1.f, ws.route_partials ? &rscratch : nullptr, &sums_done));
     IMX_CHECK_CUDA(mark(1));
     SortExtras ex;
     ex.topk_w = ws.topk_w;
@@ -350,6 +365,9 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     ga.sched = ws.sched;
     ga.partials = ws.partials;
     ga.gsum = ws.gsum;
+    ga.gsum_x = ws.gsum_x;
+    ga.n_in_rows = n_tokens;
+    ga.gsum_x_ready = sums_done ? 1 : 0;
     ga.act = ws.act;
     ga.act_stride = ws.act_stride;
     ga.row_scale = ws.w_of_slot;
@@ -523,6 +541,9 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
     ga.sched = ws.sched;
     ga.partials = ws.partials;
     ga.gsum = ws.gsum;
+    ga.gsum_x = ws.gsum_x;
+    ga.n_in_rows = n_rows;
+    ga.gsum_x_ready = 0;
     ga.act = ws.act;
     ga.act_stride = c.intermediate;
     ga.row_scale = row_scale;

@@ -289,17 +289,21 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
         const int sl = u.slot0 + (g < last ? g : last);
         const int sa = u.slot0 + (2 * t < last ? 2 * t : last), sb = u.slot0 + (2 * t + 1 < last ? 2 * t + 1 : last);
         if (SWIGLU) {
+            // rows of `in` (and of its table of group sums) behind the slots
             const int row = a.row_index ? a.row_index[sl] : sl;
+            const int ra = a.row_index ? a.row_index[sa] : sa, rb = a.row_index ? a.row_index[sb] : sb;
             c_act = a.in + (size_t)row * S.n_in + t * 16;
+            c_sum_a = a.gsum_x + (size_t)ra * sum_groups;
+            c_sum_b = a.gsum_x + (size_t)rb * sum_groups;
         } else {
             c_act = a.act + (size_t)sl * a.act_stride + t * 16;
             if (a.row_scale != nullptr) {
                 c_rs0 = a.row_scale[sa];
                 c_rs1 = a.row_scale[sb];
             }
+            c_sum_a = a.gsum + (size_t)sa * sum_groups;
+            c_sum_b = a.gsum + (size_t)sb * sum_groups;
         }
-        c_sum_a = a.gsum + (size_t)sa * sum_groups;
-        c_sum_b = a.gsum + (size_t)sb * sum_groups;
     };
     setup_unit();
     float acc[2][4];
@@ -532,11 +536,11 @@ int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn
     if (grid * kWarps > kFlagWarps) grid = kFlagWarps / kWarps;
     const int x_mid = s.has_extra ? s.x_mid : s.n_mid;
     const int mid_max = s.n_mid > x_mid ? s.n_mid : x_mid;
-    // first product: group sums of the input rows, then gate/up + SwiGLU
+    // first product: group sums of the input rows (unless the router wrote them), then gate/up + SwiGLU
     const int g_in = s.n_in / 64, g_mid = mid_max / 64;
-    {
-        const int n = a.n_slots * g_in;
-        group_sums_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a.in, a.row_index, a.n_slots, g_in, s.n_in, a.gsum);
+    if (!a.gsum_x_ready) {
+        const int n = a.n_in_rows * g_in;
+        group_sums_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a.in, nullptr, a.n_in_rows, g_in, s.n_in, a.gsum_x);
         IMX_CHECK_CUDA(cudaGetLastError());
     }
     decode_tmap_kernel<true, kWarps, kStages><<<grid, kWarps * 32, smem, stream>>>(
@@ -559,7 +563,8 @@ int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn
 
 int launch_decode_tmap(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid) {
     IMX_REQUIRE(decode_tmap_supported(a.set), "decode (tensor-map) path: format/shape not supported");
-    IMX_REQUIRE(a.partials != nullptr && a.sched != nullptr && a.gsum != nullptr && a.n_slots > 0,
+    IMX_REQUIRE(a.partials != nullptr && a.sched != nullptr && a.gsum != nullptr && a.gsum_x != nullptr && a.n_slots > 0 &&
+                    a.n_in_rows > 0,
                 "decode (tensor-map) path: workspace buffers missing");
     if (a.max_units == 0) return IMX_OK;
     const ExpertSet& s = a.set;

@@ -46,9 +46,19 @@ struct SortExtras {
     int32_t* sched = nullptr;
 };
 
+// Workspace of the split-K router (decode sizes): all pointers together or none.
+struct RouteScratch {
+    float* partials;      // [H / route_slice(H)][32 ceil(n / 32)][E] partial logits
+    float* sg_partials;   // [H / route_slice(H)][32 ceil(n / 32)] partial shared-gate dot products
+    float* gsum_x;        // [n][H / 64] group sums of the fp16 copy in units of 2^-24, or nullptr
+};
+constexpr int kRouteSplitMaxTokens = 256;   // the split-K router serves batches below this
+int route_slice(int H);                      // K slice of the split-K router (0: not applicable)
+
 int launch_route(const void* x, int n, int H, const void* Wr, const float* logit_bias, int E, int k,
                  int norm, const void* w_sg, int32_t* topk_idx, float* topk_w, float* shared_gate,
-                 void* x16, const int* order16, cudaStream_t stream, float pair_scale_odd = 1.f);
+                 void* x16, const int* order16, cudaStream_t stream, float pair_scale_odd = 1.f,
+                 const RouteScratch* rs = nullptr, bool* sums_done = nullptr);
 
 // Order of the 16 values of each block of an fp16 activation row as the
 // expert kernels of a bit width read them (identity for the generic path).
@@ -94,7 +104,10 @@ struct GroupedArgs {
     int max_units;
     int32_t* sched;                // [kSchedInts]: counters, then the hand-off flags
     float* partials;               // [kFlagWarps][8][32] fp32 hand-off slots (decode kernels)
-    float* gsum;                   // [n_slots, max(n_in, act_stride) / 64] fp32 group sums (tensor-map decode kernel)
+    float* gsum;                   // [n_slots, act_stride / 64] fp32 group sums of the SwiGLU rows (tensor-map decode kernel)
+    float* gsum_x;                 // [n_in_rows, n_in / 64] fp32 group sums of the rows of `in`
+    int n_in_rows;                 // rows of `in`
+    int gsum_x_ready;              // the router already filled gsum_x
     __half* act;                   // fp16 [n_slots, act_stride]
     int act_stride;
     const float* row_scale;        // per slot or nullptr

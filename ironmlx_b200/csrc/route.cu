@@ -55,33 +55,39 @@ __device__ void softmax_topk_warp(const float* s_logits, int E, int k, bool norm
     float my_w = 0.f;
     int my_i = 0;
     float wsum = 0.f;
-    for (int r = 0; r < k; ++r) {
-        float bv = -1.f;
-        int bi = 0x7fffffff;
+    // every lane keeps the best of its own candidates (lowest id first among equals); a round is then two
+    // warp reductions (largest probability, lowest id that has it) and a rescan in the winning lane only.
+    // Probabilities are >= 0 and the "taken" mark is -1, so the int view of the floats orders them.
+    float bv;
+    int bj;
+    auto rescan = [&]() {
+        bv = -1.f;
+        bj = 0;
 #pragma unroll
         for (int j = 0; j < JMAX; ++j) {
-            if (p[j] > bv) {           // ascending j: lower id wins ties inside a lane
+            if (p[j] > bv) {
                 bv = p[j];
-                bi = lane + 32 * j;
+                bj = j;
             }
         }
+    };
+    rescan();
+    for (int r = 0; r < k; ++r) {
+        const int mine = __float_as_int(bv);
+        const int top = __reduce_max_sync(0xffffffffu, mine);
+        const int win = __reduce_min_sync(0xffffffffu, mine == top ? lane + 32 * bj : 0x7fffffff);
+        const float wv = __int_as_float(top);
+        if (mine == top && lane + 32 * bj == win) {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) {
-                bv = ov;
-                bi = oi;
-            }
+            for (int j = 0; j < JMAX; ++j)
+                if (j == bj) p[j] = -1.f;
+            rescan();
         }
-#pragma unroll
-        for (int j = 0; j < JMAX; ++j)
-            if (lane + 32 * j == bi) p[j] = -1.f;
         if (lane == (r & 31)) {
-            my_w = bv;
-            my_i = bi;
+            my_w = wv;
+            my_i = win;
         }
-        wsum += bv;
+        wsum += wv;
         if ((r & 31) == 31 || r == k - 1) {      // flush up to 32 results
             int slot = (r & ~31) + lane;
             if (slot <= r) {
@@ -340,6 +346,167 @@ route_mma_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const
     }
 }
 
+
+// ── decode-size router on the tensor cores, split over K ────────────────────
+// One CTA per (32 experts, K slice, 32 tokens): the two bf16 tiles are copied to
+// shared memory once, multiplied with mma.sync m16n8k16, and the fp32 partial
+// logits go to the workspace; route_finish_kernel adds the slices and does
+// softmax/top-k with one warp per token.  The CTAs of expert block 0 also
+// write their K slice of the fp16 copy of x, its group sums (for the decode
+// expert kernels) and the partial shared-gate dot product.  W_r is read once
+// per token block instead of once per token.
+constexpr int kSkThreads = 128;
+
+__global__ void __launch_bounds__(kSkThreads)
+route_splitk_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const __nv_bfloat16* __restrict__ Wr,
+                    const float* __restrict__ logit_bias, int E, int k, int norm, const __nv_bfloat16* __restrict__ w_sg,
+                    int32_t* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ shared_gate,
+                    __half* __restrict__ x16, const Order16 order, int ks, const RouteScratch rs) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int pad = ks + 8;                                                          // bf16 per row: conflict-free fragment loads
+    __nv_bfloat16* s_x = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [32][pad]
+    __nv_bfloat16* s_w = s_x + 32 * pad;                                             // [32][pad]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int eb = blockIdx.x, split = blockIdx.y, tb = blockIdx.z;
+    const int n_pad = gridDim.z * 32;
+    const int tok0 = tb * 32, k0 = split * ks;
+
+    const int cpr = ks >> 3;                                                         // 16-byte pieces per row
+    for (int c = tid; c < 32 * cpr; c += kSkThreads) {
+        const int r = c / cpr, ch = c - r * cpr;
+        const int tok = tok0 + r;
+        const uint32_t dx = (uint32_t)__cvta_generic_to_shared(s_x + r * pad + ch * 8);
+        const __nv_bfloat16* sx = x + (size_t)(tok < n_tokens ? tok : 0) * H + k0 + ch * 8;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dx), "l"(sx), "r"(tok < n_tokens ? 16 : 0) : "memory");
+        const uint32_t dw = (uint32_t)__cvta_generic_to_shared(s_w + r * pad + ch * 8);
+        const __nv_bfloat16* sw = Wr + (size_t)(eb * 32 + r) * H + k0 + ch * 8;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, 16;" ::"r"(dw), "l"(sw) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
+    float acc[2][4];
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[m][i] = 0.f;
+    const __nv_bfloat16* ws = s_w + (warp * 8 + g) * pad + 2 * t;
+    for (int kk = 0; kk < ks; kk += 16) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(ws + kk);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(ws + kk + 8);
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            const __nv_bfloat16* p = s_x + (m * 16 + g) * pad + kk + 2 * t;
+            mma_bf16(acc[m], *reinterpret_cast<const uint32_t*>(p), *reinterpret_cast<const uint32_t*>(p + 8 * pad),
+                     *reinterpret_cast<const uint32_t*>(p + 8), *reinterpret_cast<const uint32_t*>(p + 8 * pad + 8), b0, b1);
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        const int e = eb * 32 + warp * 8 + 2 * t;
+        float* p = rs.partials + ((size_t)split * n_pad + tok0 + m * 16 + g) * E + e;
+        *reinterpret_cast<float2*>(p) = make_float2(acc[m][0], acc[m][1]);
+        *reinterpret_cast<float2*>(p + (size_t)8 * E) = make_float2(acc[m][2], acc[m][3]);
+    }
+
+    if (eb == 0) {
+        const int groups = H >> 6;
+        for (int r = warp * 8; r < warp * 8 + 8; ++r) {
+            const int tok = tok0 + r;
+            if (tok >= n_tokens) break;
+            const __nv_bfloat16* xr = s_x + r * pad;
+            if (x16 != nullptr) {
+                // fp16 copy of the slice in the expert kernels' order; 32 pairs = one group of 64 per pass
+                __half2* dst = reinterpret_cast<__half2*>(x16 + (size_t)tok * H + k0);
+                for (int q = 0; q < (ks >> 6); ++q) {
+                    const int i = q * 32 + lane;
+                    const int blk = (2 * i) & ~15, p = (2 * i) & 15;
+                    const float sc = (i & 1) ? order.pair_scale_odd : 1.f;
+                    const __half2 h = __halves2half2(f32_to_f16_sat(__bfloat162float(xr[blk + order.o[p]]) * sc),
+                                                     f32_to_f16_sat(__bfloat162float(xr[blk + order.o[p + 1]]) * sc));
+                    dst[i] = h;
+                    if (rs.gsum_x != nullptr) {
+                        // sum of the values the products will see, in units of 2^-24
+                        const float2 f = __half22float2(h);
+                        float v = f.x + f.y;
+                        if ((i & 1) && order.pair_scale_odd != 1.f) v *= 1.f / order.pair_scale_odd;
+                        v = warp_sum(v);
+                        if (lane == 0) rs.gsum_x[(size_t)tok * groups + (k0 >> 6) + q] = v * 5.9604644775390625e-8f;
+                    }
+                }
+            }
+            if (w_sg != nullptr) {
+                float accg = 0.f;
+                for (int c = lane * 8; c < ks; c += 256) {
+                    const uint4 xv = *reinterpret_cast<const uint4*>(xr + c);
+                    const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w_sg + k0 + c));
+                    const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv);
+                    const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 xf = __bfloat1622float2(xb[i]), wf = __bfloat1622float2(wb[i]);
+                        accg = fmaf(xf.x, wf.x, accg);
+                        accg = fmaf(xf.y, wf.y, accg);
+                    }
+                }
+                accg = warp_sum(accg);
+                if (lane == 0) rs.sg_partials[(size_t)split * n_pad + tok] = accg;
+            }
+        }
+    }
+
+}
+
+// Second half of the split-K router: one warp per token adds the K slices in slice
+// order (so the sums do not depend on timing) and does softmax / top-k.
+__global__ void __launch_bounds__(kSkThreads)
+route_finish_kernel(int n_tokens, int n_pad, int n_splits, const float* __restrict__ logit_bias, int E, int k, int norm,
+                    int has_sg, int32_t* __restrict__ topk_idx, float* __restrict__ topk_w,
+                    float* __restrict__ shared_gate, const RouteScratch rs) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* my_logits = reinterpret_cast<float*>(smem_raw) + warp * E;
+    const int tok = blockIdx.x * (kSkThreads / 32) + warp;
+    if (tok >= n_tokens) return;
+    // 4 experts per lane and pass (16-byte loads), all slices of a pass in flight together
+    for (int e = lane * 4; e < E; e += 128) {
+        const float* p = rs.partials + (size_t)tok * E + e;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {
+            float4 part[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                part[u] = s0 + u < n_splits ? __ldcg(reinterpret_cast<const float4*>(p + (size_t)(s0 + u) * n_pad * E))
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                v.x += part[u].x; v.y += part[u].y; v.z += part[u].z; v.w += part[u].w;
+            }
+        }
+        if (logit_bias != nullptr) {
+            v.x += logit_bias[e]; v.y += logit_bias[e + 1]; v.z += logit_bias[e + 2]; v.w += logit_bias[e + 3];
+        }
+        *reinterpret_cast<float4*>(my_logits + e) = v;
+    }
+    __syncwarp();
+    int32_t* oi = topk_idx + (size_t)tok * k;
+    float* ow = topk_w + (size_t)tok * k;
+    const int j = (E + 31) / 32;
+    if (j <= 1) softmax_topk_warp<1>(my_logits, E, k, norm, oi, ow);
+    else if (j <= 2) softmax_topk_warp<2>(my_logits, E, k, norm, oi, ow);
+    else if (j <= 4) softmax_topk_warp<4>(my_logits, E, k, norm, oi, ow);
+    else if (j <= 8) softmax_topk_warp<8>(my_logits, E, k, norm, oi, ow);
+    else if (j <= 16) softmax_topk_warp<16>(my_logits, E, k, norm, oi, ow);
+    else softmax_topk_warp<32>(my_logits, E, k, norm, oi, ow);
+    if (has_sg && lane == 0) {
+        float v = 0.f;
+        for (int s = 0; s < n_splits; ++s) v += __ldcg(rs.sg_partials + (size_t)s * n_pad + tok);
+        shared_gate[tok] = 1.0f / (1.0f + expf(-v));
+    }
+}
+
 template <int NT>
 int launch_route_mma(const void* x, int n, int H, const void* Wr, const float* logit_bias, int k, int norm,
                      const void* w_sg, int32_t* topk_idx, float* topk_w, float* shared_gate, void* x16,
@@ -358,9 +525,17 @@ int launch_route_mma(const void* x, int n, int H, const void* Wr, const float* l
 
 }  // namespace
 
+int route_slice(int H) {
+    if (H % 256 == 0 && H / 256 <= 32) return 256;
+    if (H % 128 == 0 && H / 128 <= 32) return 128;
+    if (H % 64 == 0 && H / 64 <= 32) return 64;
+    return 0;
+}
+
 int launch_route(const void* x, int n, int H, const void* Wr, const float* logit_bias, int E, int k,
                  int norm, const void* w_sg, int32_t* topk_idx, float* topk_w, float* shared_gate,
-                 void* x16, const int* order16, cudaStream_t stream, float pair_scale_odd) {
+                 void* x16, const int* order16, cudaStream_t stream, float pair_scale_odd, const RouteScratch* rs,
+                 bool* sums_done) {
     IMX_REQUIRE(n >= 0 && H > 0 && H % 16 == 0, "route: hidden (%d) must be a positive multiple of 16", H);
     Order16 order;
     for (int i = 0; i < 16; ++i) order.o[i] = (int8_t)(order16 ? order16[i] : i);
@@ -368,7 +543,22 @@ int launch_route(const void* x, int n, int H, const void* Wr, const float* logit
     IMX_REQUIRE(E >= 1 && E <= 1024, "route: num_experts (%d) must be in 1..1024", E);
     IMX_REQUIRE(k >= 1 && k <= E, "route: top_k (%d) must be in 1..num_experts (%d)", k, E);
     IMX_REQUIRE(w_sg == nullptr || shared_gate != nullptr, "route: shared gate weight without output");
+    if (sums_done != nullptr) *sums_done = false;
     if (n == 0) return IMX_OK;
+    const int ks = route_slice(H);
+    if (rs != nullptr && rs->partials != nullptr && n < kRouteSplitMaxTokens && ks > 0 && E % 32 == 0 && x16 != nullptr) {
+        const size_t tiles = (size_t)2 * 32 * (ks + 8) * sizeof(__nv_bfloat16);
+        const dim3 grid((unsigned)(E / 32), (unsigned)(H / ks), (unsigned)ceil_div(n, 32));
+        route_splitk_kernel<<<grid, kSkThreads, tiles, stream>>>(
+            (const __nv_bfloat16*)x, n, H, (const __nv_bfloat16*)Wr, logit_bias, E, k, norm, (const __nv_bfloat16*)w_sg,
+            topk_idx, topk_w, shared_gate, (__half*)x16, order, ks, *rs);
+        IMX_CHECK_CUDA(cudaGetLastError());
+        route_finish_kernel<<<ceil_div(n, kSkThreads / 32), kSkThreads, (size_t)(kSkThreads / 32) * E * sizeof(float), stream>>>(
+            n, (int)grid.z * 32, (int)grid.y, logit_bias, E, k, norm, w_sg != nullptr, topk_idx, topk_w, shared_gate, *rs);
+        IMX_CHECK_CUDA(cudaGetLastError());
+        if (sums_done != nullptr) *sums_done = rs->gsum_x != nullptr;
+        return IMX_OK;
+    }
     if (n >= 256 && H % kRK == 0 && E % 32 == 0 && E <= 256) {
         switch (E / 32) {
             case 1: return launch_route_mma<1>(x, n, H, Wr, logit_bias, k, norm, w_sg, topk_idx, topk_w, shared_gate, x16, order, stream);

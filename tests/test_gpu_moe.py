@@ -219,6 +219,27 @@ def test_decode_tensor_map_skew_and_empty(cuda):
     compare(cfg, x, p, y, tr)
 
 
+@pytest.mark.parametrize("cfg", [
+    MoEConfig("rt-e32-h192", 31, 192, 32, 4, 128, 128, seed=41),          # K slices of 64
+    MoEConfig("rt-e64-h384", 1, 384, 64, 6, 128, 128, seed=42),           # K slices of 128, one token
+    MoEConfig("rt-e64-h512", 255, 512, 64, 8, 512, 512, seed=43),         # 8 token blocks, last one ragged
+    MoEConfig("rt-e256-h256", 70, 256, 256, 8, 128, 0, seed=44),          # no shared expert
+    MoEConfig("rt-e96-nonorm", 33, 512, 96, 5, 512, 512, norm_topk_prob=False, seed=45),
+], ids=lambda c: c.name)
+def test_split_k_router(cuda, cfg):
+    """Batches below 256 tokens with a multiple of 32 experts take the split-K tensor-core router inside
+    the fused forward: expert sets, weights, shared gate and the fp16 copy all feed the block output."""
+    x, p = make_params(cfg)
+    p.router_logit_bias = np.zeros(cfg.num_experts, np.float32)
+    p.router_logit_bias[::3] = 0.25
+    x, p, moe, y, tr = run(cfg, cuda, "auto", x, p)
+    compare(cfg, x, p, y, tr)
+    y2, tr2 = moe.forward_with_stream(t_bf16(x, cuda), trace=True)        # same workspace: the counters were left clean
+    torch.cuda.synchronize()
+    moe.check_status()
+    assert np.array_equal(tr["topk_idx"], tr2["topk_idx"].cpu().numpy()) and np.array_equal(y, bf16_to_np(y2))
+
+
 def test_c2_reduced_experts(cuda):
     """The decode benchmark shape with 32 of the 256 experts (the checker
     finishes in seconds), 64 tokens, top-8, shared expert."""
