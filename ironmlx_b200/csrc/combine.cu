@@ -21,19 +21,21 @@ __global__ void __launch_bounds__(kCThreads)
 combine_kernel(const float* __restrict__ rows, const float* __restrict__ row_scale,
                const int32_t* __restrict__ inv_perm, int k, int H, const float* __restrict__ shared_rows,
                void* __restrict__ y_out) {
+    __shared__ int s_raw[kMaxK];
     __shared__ int s_slot[kMaxK];
     const int t = blockIdx.x;
     const int tid = threadIdx.x;
-    if (tid == 0) {
-        for (int s = 0; s < k; ++s) {            // insertion sort, k is tiny
-            int v = inv_perm[(size_t)t * k + s];
-            int j = s;
-            while (j > 0 && s_slot[j - 1] > v) {
-                s_slot[j] = s_slot[j - 1];
-                --j;
-            }
-            s_slot[j] = v;
+    // the token's k slots in ascending order: one load per thread, then a rank sort (k is tiny)
+    if (tid < k) s_raw[tid] = inv_perm[(size_t)t * k + tid];
+    __syncthreads();
+    if (tid < k) {
+        const int v = s_raw[tid];
+        int rank = 0;
+        for (int j = 0; j < k; ++j) {
+            const int o = s_raw[j];
+            rank += (o < v) || (o == v && j < tid);
         }
+        s_slot[rank] = v;
     }
     __syncthreads();
     const int c = blockIdx.y * kCCols + tid * 4;

@@ -215,6 +215,68 @@ sort_fused_kernel(const int32_t* __restrict__ ids, int A, int E, int32_t* __rest
     emit_aux(aux, perm, s_off, E, A, s_warp);
 }
 
+// One block, at most one id per thread (A <= kSortThreads, E <= kSmallSortExperts): ids are read
+// once, ranks stay in registers, and every output is written once (decode-size batches).
+constexpr int kSmallSortExperts = 256;
+
+__global__ void __launch_bounds__(kSortThreads)
+sort_small_kernel(const int32_t* __restrict__ ids, int A, int E, int32_t* __restrict__ counts,
+                  int32_t* __restrict__ offsets, int32_t* __restrict__ perm,
+                  int32_t* __restrict__ inv_perm, SortAux aux) {
+    extern __shared__ int s_mem[];
+    int* s_hist = s_mem;                       // [kSortWarps][E]
+    int* s_tot = s_hist + kSortWarps * E;      // [E]
+    int* s_off = s_tot + E;                    // [E+1]
+    int* s_warp = s_off + E + 1;               // [33]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int e = tid < A ? ids[tid] : -1;
+    if (e < 0 || e >= E) e = -1;                          // moe.rs:100: out-of-range ids are dropped
+    const float w = (tid < A && aux.topk_w != nullptr) ? aux.topk_w[tid] : 1.f;
+    const int n_warps = (A + 31) >> 5;
+    for (int i = tid; i < n_warps * E; i += kSortThreads) s_hist[i] = 0;
+    __syncthreads();
+    // rank among equal ids inside the warp; the first lane of every group leaves the group's size
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    int rank = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank == 0) s_hist[warp * E + e] = __popc(peers);
+    __syncthreads();
+    for (int x = tid; x < E; x += kSortThreads) {          // exclusive scan over warps, per expert
+        int run = 0;
+        for (int v = 0; v < n_warps; ++v) {
+            const int c = s_hist[v * E + x];
+            s_hist[v * E + x] = run;
+            run += c;
+        }
+        s_tot[x] = run;
+        if (counts != nullptr) counts[x] = run;
+    }
+    __syncthreads();
+    if (e >= 0) rank += s_hist[warp * E + e];
+    scan_experts(s_tot, E, offsets, s_off, s_warp);
+    if (tid < A) {
+        if (e >= 0) {
+            const int pos = s_off[e] + rank;
+            perm[pos] = tid;
+            inv_perm[tid] = pos;
+            if (aux.tok_of_slot != nullptr) {
+                aux.tok_of_slot[pos] = tid / aux.top_k;
+                if (aux.w_of_slot) aux.w_of_slot[pos] = w;
+            }
+        } else {
+            inv_perm[tid] = -1;
+        }
+    }
+    if (aux.tok_of_slot != nullptr && aux.shared_gate != nullptr) {
+        for (int t = tid; t < aux.n_tokens; t += kSortThreads) {
+            aux.tok_of_slot[A + t] = t;
+            if (aux.w_of_slot) aux.w_of_slot[A + t] = aux.shared_gate[t];
+        }
+    }
+    SortAux rest = aux;
+    rest.tok_of_slot = nullptr;                           // written above; what remains: unit list, scheduler reset
+    emit_aux(rest, nullptr, s_off, E, A, s_warp);
+}
+
 // Multi-block path, launch 1: ranks inside each block + per-block totals.
 __global__ void __launch_bounds__(kSortThreads)
 sort_rank_kernel(const int32_t* __restrict__ ids, int A, int E, int32_t* __restrict__ rank_tmp,
@@ -346,6 +408,11 @@ int launch_sort(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offs
         IMX_REQUIRE(aux.units == nullptr || E + 1 <= kSortThreads, "sort: too many experts for the unit list");
     }
     const size_t smem_fused = ((size_t)kSortWarps * E + E + E + 1 + 33) * sizeof(int);
+    if (A <= kSortThreads && E <= kSmallSortExperts) {
+        sort_small_kernel<<<1, kSortThreads, smem_fused, stream>>>(ids, A, E, counts, offsets, perm, inv_perm, aux);
+        IMX_CHECK_CUDA(cudaGetLastError());
+        return IMX_OK;
+    }
     if (A <= kSortChunk) {
         IMX_CHECK_CUDA(cudaFuncSetAttribute(sort_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             (int)smem_fused));

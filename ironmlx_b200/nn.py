@@ -189,6 +189,12 @@ class MoEMLP:
                                     ws.numel(), ops.stream_ptr(stream), None if tr is None else C.byref(tr)))
         return (y, tensors) if trace else y
 
+    def capture(self, x: torch.Tensor) -> "CapturedForward":
+        """The block for a fixed input buffer as a CUDA graph: every kernel of
+        `forward_with_stream(x)` recorded once and replayed with one launch
+        (decode loops call the block with the same shapes every step)."""
+        return CapturedForward(self, x)
+
     def forward_timed(self, x: torch.Tensor, stream=None):
         """-> (y, [router, sort, gate/up, down, combine] milliseconds), measured
         with CUDA events recorded between the stages on the stream."""
@@ -216,6 +222,33 @@ class MoEMLP:
     def check_status(self, stream=None) -> None:
         if self._workspace is not None:
             check(lib().imx_moe_status(self._workspace.data_ptr(), ops.stream_ptr(stream)))
+
+
+class CapturedForward:
+    """CUDA-graph replay of `MoEMLP.forward_with_stream` on static buffers:
+    write the step's activations into `x` (or pass them to `__call__`, which
+    copies), call, read `y`.  The graph holds the block's workspace, so one
+    instance serves one stream of steps at a time."""
+
+    def __init__(self, moe: "MoEMLP", x: torch.Tensor):
+        self.moe = moe
+        self.x = x.contiguous().clone()
+        side = torch.cuda.Stream(device=x.device)
+        side.wait_stream(torch.cuda.current_stream(x.device))
+        with torch.cuda.stream(side):                    # warm up off the capture: attributes, workspace
+            for _ in range(2):
+                moe.forward_with_stream(self.x)
+        torch.cuda.current_stream(x.device).wait_stream(side)
+        torch.cuda.synchronize(x.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.y = moe.forward_with_stream(self.x)
+
+    def __call__(self, x: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if x is not None and x.data_ptr() != self.x.data_ptr():
+            self.x.copy_(x, non_blocking=True)
+        self.graph.replay()
+        return self.y
 
 
 @dataclass
