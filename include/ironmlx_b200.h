@@ -161,6 +161,18 @@ IMX_API int imx_moe_route(const void* x, int n_tokens, int hidden, const void* r
                   const void* shared_gate_w, int32_t* topk_idx, float* topk_w,
                   float* shared_gate, void* x_f16, void* stream);
 
+/* The same stage with caller-provided scratch (imx_moe_route_scratch_bytes bytes, 256-byte aligned):
+ * batches below 1024 tokens with a multiple of 32 experts then take the split-K
+ * tensor-core router, which reads router_w once per 32 tokens instead of once per
+ * token.  Results are the same as imx_moe_route's up to the summation order of
+ * the logits. */
+IMX_API int imx_moe_route_scratch_bytes(int n_tokens, int hidden, int num_experts, size_t* bytes);
+IMX_API int imx_moe_route_ws(const void* x, int n_tokens, int hidden, const void* router_w,
+                     const float* logit_bias, int num_experts, int top_k, int norm_topk_prob,
+                     const void* shared_gate_w, int32_t* topk_idx, float* topk_w,
+                     float* shared_gate, void* x_f16, void* scratch, size_t scratch_bytes,
+                     void* stream);
+
 /* Bucketing (moe.rs:93-104) as a stable counting sort of the n_assign =
  * N*k expert ids: counts[E], offsets[E+1], perm[n_assign], inv_perm[n_assign].
  * scratch: imx_moe_sort_scratch_bytes(n_assign, E) bytes. */

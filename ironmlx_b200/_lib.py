@@ -52,6 +52,8 @@ SIGNATURES = {
     "imx_moe_forward_host": (_i, [C.POINTER(MoEConfig), C.POINTER(MoEWeights), _vp, _i, _vp, _vp, _sz, _vp]),
     "imx_moe_status": (_i, [_vp, _vp]),
     "imx_moe_route": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "imx_moe_route_scratch_bytes": (_i, [_i, _i, _i, C.POINTER(_sz)]),
+    "imx_moe_route_ws": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "imx_moe_sort_scratch_bytes": (_i, [_i, _i, C.POINTER(_sz)]),
     "imx_moe_sort": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "imx_moe_sort_static": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),

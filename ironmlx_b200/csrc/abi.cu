@@ -281,6 +281,26 @@ __global__ void permute_rows_kernel(const __half* __restrict__ src, const int32_
 }
 }  // namespace
 
+namespace {
+struct RouteWs {
+    float* partials;
+    float* sg;
+    size_t bytes;
+};
+RouteWs carve_route(int n, int hidden, int num_experts, void* base) {
+    RouteWs w = {};
+    Carver cv(base);
+    const int slice = route_slice(hidden);
+    if (n > 0 && n < kRouteSplitMaxTokens && slice > 0 && num_experts % 32 == 0) {
+        const size_t splits = (size_t)hidden / slice, n_pad = (size_t)(n + 31) / 32 * 32;
+        w.partials = cv.take<float>(splits * n_pad * num_experts);
+        w.sg = cv.take<float>(splits * n_pad);
+    }
+    w.bytes = align_up(cv.off, 256);
+    return w;
+}
+}  // namespace
+
 }  // namespace imx
 
 using namespace imx;
@@ -463,6 +483,30 @@ int imx_moe_route(const void* x, int n_tokens, int hidden, const void* router_w,
     IMX_REQUIRE(x && router_w && topk_idx && topk_w, "route: x, router_w, topk_idx and topk_w are required");
     return launch_route(x, n_tokens, hidden, router_w, logit_bias, num_experts, top_k, norm_topk_prob,
                         shared_gate_w, topk_idx, topk_w, shared_gate, x_f16, nullptr, (cudaStream_t)stream);
+}
+
+int imx_moe_route_scratch_bytes(int n_tokens, int hidden, int num_experts, size_t* bytes) {
+    using namespace imx;
+    IMX_REQUIRE(bytes != nullptr && n_tokens >= 0 && hidden > 0 && num_experts >= 1, "route_scratch_bytes: bad arguments");
+    *bytes = carve_route(n_tokens, hidden, num_experts, nullptr).bytes;
+    return IMX_OK;
+}
+
+int imx_moe_route_ws(const void* x, int n_tokens, int hidden, const void* router_w, const float* logit_bias,
+                     int num_experts, int top_k, int norm_topk_prob, const void* shared_gate_w,
+                     int32_t* topk_idx, float* topk_w, float* shared_gate, void* x_f16, void* scratch,
+                     size_t scratch_bytes, void* stream) {
+    using namespace imx;
+    IMX_REQUIRE(n_tokens >= 0, "route: negative token count");
+    if (n_tokens == 0) return IMX_OK;
+    IMX_REQUIRE(x && router_w && topk_idx && topk_w, "route: x, router_w, topk_idx and topk_w are required");
+    RouteWs ws = carve_route(n_tokens, hidden, num_experts, scratch);
+    IMX_REQUIRE(ws.bytes == 0 || (scratch != nullptr && ((uintptr_t)scratch % 256) == 0 && scratch_bytes >= ws.bytes),
+                "route: scratch of %zu bytes (256-byte aligned) needed, %zu given", ws.bytes, scratch_bytes);
+    RouteScratch rs = {ws.partials, ws.sg, nullptr};
+    return launch_route(x, n_tokens, hidden, router_w, logit_bias, num_experts, top_k, norm_topk_prob,
+                        shared_gate_w, topk_idx, topk_w, shared_gate, x_f16, nullptr, (cudaStream_t)stream, 1.f,
+                        ws.partials ? &rs : nullptr, nullptr);
 }
 
 int imx_moe_sort_scratch_bytes(int n_assign, int num_experts, size_t* bytes) {

@@ -20,8 +20,9 @@
 //     down to 2^-10; Order16::pair_scale_odd).  The fold per group is
 //     acc += s*D + b*sum(x) with everything in units of 2^-24, and the epilogue
 //     multiplies by 2^24.
-//   * sum(x) * 2^-24 per (slot, group) comes from a table written by a small kernel
-//     before each product (group_sums_kernel), read two groups at a time.
+//   * sum(x) * 2^-24 per (row, group): for the first product a table written by the
+//     router (or by group_sums_kernel), for the second each warp sums the groups
+//     of its unit's SwiGLU rows into shared memory when it reaches the unit.
 //   * activations and table entries of the next 128 codes are loaded while the
 //     current 128 are multiplied (register double buffer), across stage
 //     boundaries too.
@@ -31,9 +32,6 @@
 // warps is finished by the warp that owns its first stage, the others hand their
 // fp32 partial sums over through the workspace.  Every wait is bounded.
 #include <cuda.h>
-
-#include <cstdio>
-#include <cstdlib>
 
 #include "decode_common.cuh"
 
@@ -48,8 +46,9 @@ constexpr int kWBytes = 2 * 16 * 128;          // packed codes of a stage: one b
 constexpr int kSBytes = 4 * 16 * 16;           // scales, biases of tile 0, then of tile 1: 16 rows x 8 groups x 2 bytes
 // shared memory of a CTA of `warps` warps with `stages` stages each: codes | scales+biases | barriers (+ slack to
 // align the base to 1024 bytes)
-constexpr size_t smem_bytes(int warps, int stages) {
-    return (size_t)warps * stages * (kWBytes + kSBytes + 8) + 1024;
+constexpr int kMaxSumGroups = 64;              // second product: groups of 64 per SwiGLU row (intermediate <= 4096)
+constexpr size_t smem_bytes(int warps, int stages, bool with_sums) {
+    return (size_t)warps * stages * (kWBytes + kSBytes + 8) + (with_sums ? (size_t)warps * 8 * kMaxSumGroups * 4 : 0) + 1024;
 }
 constexpr int kSpinLimit = 1 << 20;
 constexpr int kFlagSpinLimit = 1 << 22;
@@ -167,6 +166,8 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
     const uint32_t wbuf = sbase + (uint32_t)warp * (kStages * kWBytes);
     const uint32_t sbuf = sbase + kSmemW + (uint32_t)warp * (kStages * kSBytes);
     const uint32_t bars = sbase + kSmemW + kSmemS + (uint32_t)warp * (kStages * 8);
+    // second product only: group sums of the unit's SwiGLU rows, [8 slots][kMaxSumGroups]
+    const uint32_t sums = sbase + kSmemW + kSmemS + kWarps * kStages * 8 + (uint32_t)warp * (8 * kMaxSumGroups * 4);
 
     const int n_r = a.n_units[1];
     const int stages_r = n_r * ppu_r * st_r;
@@ -277,8 +278,9 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
     int c_st_lo = start.st;             // stage of its pair at which the current piece began
     int c_unit = -1, c_rows = 0, c_slot0 = 0;
     const __half* c_act = nullptr;      // this lane's activation row (slot g of the unit, clamped to a valid slot)
-    const float* c_sum_a = nullptr;     // group sums of slots 2t and 2t+1 (clamped likewise)
+    const float* c_sum_a = nullptr;     // first product: group sums of slots 2t and 2t+1 (clamped likewise)
     const float* c_sum_b = nullptr;
+    uint32_t c_sums_a = 0, c_sums_b = 0; // second product: the same two rows in this warp's shared-memory table
     float c_rs0 = 1.f, c_rs1 = 1.f;     // output scale of slots 2t, 2t+1 (second product)
     auto setup_unit = [&]() {
         c_unit = cc.unit;
@@ -301,8 +303,33 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
                 c_rs0 = a.row_scale[sa];
                 c_rs1 = a.row_scale[sb];
             }
-            c_sum_a = a.gsum + (size_t)sa * sum_groups;
-            c_sum_b = a.gsum + (size_t)sb * sum_groups;
+            // Group sums of the unit's rows, in units of 2^-24, into the warp's table: lane L takes
+            // slot L / 4 and every fourth group from L % 4.  Pairs 1 and 3 of every 8 stored values hold x / 16.
+            const int groups = (cc.extra ? S.x_mid : S.n_mid) >> 6;
+            __syncwarp();
+            if (g < u.rows) {
+                const __half* row = a.act + (size_t)(u.slot0 + g) * a.act_stride;
+                for (int grp = t; grp < groups; grp += 4) {
+                    const uint4* p = reinterpret_cast<const uint4*>(row + grp * 64);
+                    float lo = 0.f, hi = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint4 v = __ldg(p + i);
+                        const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w4[e]));
+                            if (e & 1) hi += f.x + f.y;
+                            else lo += f.x + f.y;
+                        }
+                    }
+                    const float v = (lo + 16.f * hi) * 5.9604644775390625e-8f;
+                    asm volatile("st.shared.f32 [%0], %1;" ::"r"(sums + (uint32_t)(g * kMaxSumGroups + grp) * 4u), "f"(v) : "memory");
+                }
+            }
+            __syncwarp();
+            c_sums_a = sums + (uint32_t)((sa - u.slot0) * kMaxSumGroups) * 4u;
+            c_sums_b = sums + (uint32_t)((sb - u.slot0) * kMaxSumGroups) * 4u;
         }
     };
     setup_unit();
@@ -410,8 +437,14 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
         bf[buf][4] = v1.x; bf[buf][5] = v1.y; bf[buf][6] = v1.z; bf[buf][7] = v1.w;
     };
     auto load_sums = [&]() {
-        const uint4 va = ldg128_early(reinterpret_cast<const uint4*>(c_sum_a + cc.st * 4));
-        const uint4 vb = ldg128_early(reinterpret_cast<const uint4*>(c_sum_b + cc.st * 4));
+        uint4 va, vb;
+        if (SWIGLU) {
+            va = ldg128_early(reinterpret_cast<const uint4*>(c_sum_a + cc.st * 4));
+            vb = ldg128_early(reinterpret_cast<const uint4*>(c_sum_b + cc.st * 4));
+        } else {
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(va.x), "=r"(va.y), "=r"(va.z), "=r"(va.w) : "r"(c_sums_a + (uint32_t)cc.st * 16u));
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(vb.x), "=r"(vb.y), "=r"(vb.z), "=r"(vb.w) : "r"(c_sums_b + (uint32_t)cc.st * 16u));
+        }
         sxa[0] = __uint_as_float(va.x); sxa[1] = __uint_as_float(va.y); sxa[2] = __uint_as_float(va.z); sxa[3] = __uint_as_float(va.w);
         sxb[0] = __uint_as_float(vb.x); sxb[1] = __uint_as_float(vb.y); sxb[2] = __uint_as_float(vb.z); sxb[3] = __uint_as_float(vb.w);
     };
@@ -503,17 +536,15 @@ bool decode_tmap_supported(const ExpertSet& s) {
     if (f.mode != IMX_MODE_AFFINE || f.bits != 4 || f.group != 64) return false;
     if (s.n_in % 512 || s.n_mid % 512) return false;
     if (s.has_extra && s.x_mid % 512) return false;
+    if (s.n_mid > 64 * kMaxSumGroups || (s.has_extra && s.x_mid > 64 * kMaxSumGroups)) return false;
     return true;
 }
 
 namespace {
 
-bool g_promote256 = false;
-
 int make_maps(const QMat& m, size_t rows, int K, CUtensorMap* w, CUtensorMap* sc, CUtensorMap* bi) {
     const size_t groups = (size_t)K / 64;
-    IMX_TRY(make_tensor_map_2d(m.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, (size_t)K / 2, (size_t)K / 2, 128, 16, true, w,
-                               g_promote256));
+    IMX_TRY(make_tensor_map_2d(m.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, (size_t)K / 2, (size_t)K / 2, 128, 16, true, w));
     IMX_TRY(make_tensor_map_2d(m.scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, rows, groups, groups * 2, 8, 16, false, sc));
     IMX_TRY(make_tensor_map_2d(m.biases, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, rows, groups, groups * 2, 8, 16, false, bi));
     return IMX_OK;
@@ -523,13 +554,13 @@ template <int kWarps, int kStages>
 int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn, int sms, cudaStream_t stream,
                 cudaEvent_t mid) {
     const ExpertSet& s = a.set;
-    constexpr size_t smem = smem_bytes(kWarps, kStages);
+    constexpr size_t smem_gu = smem_bytes(kWarps, kStages, false), smem_dn = smem_bytes(kWarps, kStages, true);
     static bool configured = false;
     if (!configured) {
         IMX_CHECK_CUDA(cudaFuncSetAttribute(decode_tmap_kernel<true, kWarps, kStages>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_gu));
         IMX_CHECK_CUDA(cudaFuncSetAttribute(decode_tmap_kernel<false, kWarps, kStages>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dn));
         configured = true;
     }
     int grid = sms;
@@ -543,17 +574,12 @@ int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn
         group_sums_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a.in, nullptr, a.n_in_rows, g_in, s.n_in, a.gsum_x);
         IMX_CHECK_CUDA(cudaGetLastError());
     }
-    decode_tmap_kernel<true, kWarps, kStages><<<grid, kWarps * 32, smem, stream>>>(
+    decode_tmap_kernel<true, kWarps, kStages><<<grid, kWarps * 32, smem_gu, stream>>>(
         a, s.n_mid / 16, x_mid / 16, s.n_in / kStageCodes, s.n_in / kStageCodes, 8, g_in, gu);
     IMX_CHECK_CUDA(cudaGetLastError());
     if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
-    // second product: group sums of the SwiGLU rows, then down
-    {
-        const int n = a.n_slots * g_mid;
-        group_sums_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a.act, nullptr, a.n_slots, g_mid, a.act_stride, a.gsum);
-        IMX_CHECK_CUDA(cudaGetLastError());
-    }
-    decode_tmap_kernel<false, kWarps, kStages><<<grid, kWarps * 32, smem, stream>>>(
+    // second product: every warp sums the groups of its unit's SwiGLU rows itself
+    decode_tmap_kernel<false, kWarps, kStages><<<grid, kWarps * 32, smem_dn, stream>>>(
         a, s.n_in / 32, s.n_in / 32, s.n_mid / kStageCodes, x_mid / kStageCodes, 8 + kFlagWarps, g_mid, dn);
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
@@ -563,20 +589,16 @@ int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn
 
 int launch_decode_tmap(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid) {
     IMX_REQUIRE(decode_tmap_supported(a.set), "decode (tensor-map) path: format/shape not supported");
-    IMX_REQUIRE(a.partials != nullptr && a.sched != nullptr && a.gsum != nullptr && a.gsum_x != nullptr && a.n_slots > 0 &&
+    IMX_REQUIRE(a.partials != nullptr && a.sched != nullptr && a.gsum_x != nullptr && a.n_slots > 0 &&
                     a.n_in_rows > 0,
                 "decode (tensor-map) path: workspace buffers missing");
     if (a.max_units == 0) return IMX_OK;
     const ExpertSet& s = a.set;
-    static int sms = 0, variant = 0;
+    static int sms = 0;
     if (sms == 0) {
         int dev = 0, v = 0;
         IMX_CHECK_CUDA(cudaGetDevice(&dev));
         IMX_CHECK_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
-        const char* e = getenv("IMX_DECODE_VARIANT");
-        variant = e ? atoi(e) : 0;
-        g_promote256 = (variant & 4) != 0;
-        variant &= 3;
         sms = v;
     }
     DecodeMaps gu, dn;
@@ -591,9 +613,7 @@ int launch_decode_tmap(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mi
         dn.w[1] = dn.w[0]; dn.s[1] = dn.s[0]; dn.b[1] = dn.b[0];
     }
     dn.w[2] = dn.w[1]; dn.s[2] = dn.s[1]; dn.b[2] = dn.b[1];
-    if (variant == 1) return launch_with<12, 3>(a, gu, dn, sms, stream, mid);
-    if (variant == 2) return launch_with<20, 2>(a, gu, dn, sms, stream, mid);
-    if (variant == 3) return launch_with<14, 3>(a, gu, dn, sms, stream, mid);
+    // 16 warps x 2 stages: measured best on B200 against 12 x 3, 14 x 3 and 20 x 2 (which spills at 96 registers)
     return launch_with<16, 2>(a, gu, dn, sms, stream, mid);
 }
 

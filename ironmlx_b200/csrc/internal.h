@@ -52,7 +52,7 @@ struct RouteScratch {
     float* sg_partials;   // [H / route_slice(H)][32 ceil(n / 32)] partial shared-gate dot products
     float* gsum_x;        // [n][H / 64] group sums of the fp16 copy in units of 2^-24, or nullptr
 };
-constexpr int kRouteSplitMaxTokens = 256;   // the split-K router serves batches below this
+constexpr int kRouteSplitMaxTokens = 1024;   // the split-K router serves batches below this
 int route_slice(int H);                      // K slice of the split-K router (0: not applicable)
 
 int launch_route(const void* x, int n, int H, const void* Wr, const float* logit_bias, int E, int k,

@@ -70,10 +70,14 @@ class CudaStages:
         w = torch.empty(n, k, dtype=torch.float32, device=x.device)
         sg = torch.empty(n, dtype=torch.float32, device=x.device)
         x16 = torch.empty(n, h, dtype=torch.float16, device=x.device)
-        check(lib().imx_moe_route(x.data_ptr(), n, h, router_w.data_ptr(),
-                                  None if logit_bias is None else logit_bias.data_ptr(), e, k, int(norm),
-                                  None if shared_gate_w is None else shared_gate_w.data_ptr(), idx.data_ptr(),
-                                  w.data_ptr(), sg.data_ptr(), x16.data_ptr(), ops.stream_ptr()))
+        nb = C.c_size_t(0)
+        check(lib().imx_moe_route_scratch_bytes(n, h, e, C.byref(nb)))
+        scratch = self._buf("route", nb.value)
+        check(lib().imx_moe_route_ws(x.data_ptr(), n, h, router_w.data_ptr(),
+                                     None if logit_bias is None else logit_bias.data_ptr(), e, k, int(norm),
+                                     None if shared_gate_w is None else shared_gate_w.data_ptr(), idx.data_ptr(),
+                                     w.data_ptr(), sg.data_ptr(), x16.data_ptr(), scratch.data_ptr(),
+                                     scratch.numel(), ops.stream_ptr()))
         return idx, w, sg, x16
 
     def sort(self, ids, num_experts):

@@ -19,7 +19,7 @@ FORMATS = [("affine", 2, 64), ("affine", 3, 32), ("affine", 4, 64), ("affine", 4
            ("affine", 6, 128), ("affine", 8, 64), ("affine", 8, 32), ("mxfp8", 8, 32), ("nvfp4", 4, 16)]
 
 
-def run_route(x, p, k, norm, dev, bias=None):
+def run_route(x, p, k, norm, dev, bias=None, ws=False):
     n, h = x.shape
     e = p.router_w.shape[0]
     xd, wr = t_bf16(x, dev), t_bf16(p.router_w, dev)
@@ -29,9 +29,15 @@ def run_route(x, p, k, norm, dev, bias=None):
     sg = torch.empty(n, device=dev)
     x16 = torch.empty(n, h, dtype=torch.float16, device=dev)
     bd = None if bias is None else torch.from_numpy(bias).to(dev)
-    _lib.check(_lib.lib().imx_moe_route(xd.data_ptr(), n, h, wr.data_ptr(), None if bd is None else bd.data_ptr(),
-                                        e, k, int(norm), None if wsg is None else wsg.data_ptr(), idx.data_ptr(),
-                                        w.data_ptr(), sg.data_ptr(), x16.data_ptr(), ops.stream_ptr()))
+    args = (xd.data_ptr(), n, h, wr.data_ptr(), None if bd is None else bd.data_ptr(), e, k, int(norm),
+            None if wsg is None else wsg.data_ptr(), idx.data_ptr(), w.data_ptr(), sg.data_ptr(), x16.data_ptr())
+    if ws:      # the entry point with scratch: split-K tensor-core router where it applies
+        nb = C.c_size_t(0)
+        _lib.check(_lib.lib().imx_moe_route_scratch_bytes(n, h, e, C.byref(nb)))
+        scratch = torch.empty(max(nb.value, 256), dtype=torch.uint8, device=dev)
+        _lib.check(_lib.lib().imx_moe_route_ws(*args, scratch.data_ptr(), scratch.numel(), ops.stream_ptr()))
+    else:
+        _lib.check(_lib.lib().imx_moe_route(*args, ops.stream_ptr()))
     torch.cuda.synchronize()
     return idx.cpu().numpy(), w.cpu().numpy(), sg.cpu().numpy(), x16.cpu().numpy()
 
@@ -56,7 +62,8 @@ def check_routing(idx, w, x, p, k, norm, bias=None):
                                  MoEConfig("r300", 300, 1024, 128, 6, 64, 0, seed=2),
                                  MoEConfig("odd", 7, 256, 48, 5, 64, 64, norm_topk_prob=False, seed=5),
                                  MoEConfig("one", 1, 128, 4, 4, 64, 0, seed=6)], ids=lambda c: c.name)
-def test_route_matches_checker(cuda, cfg):
+@pytest.mark.parametrize("ws", [False, True], ids=["plain", "scratch"])
+def test_route_matches_checker(cuda, cfg, ws):
     wl_cfg = cfg.with_(intermediate=64, shared_intermediate=min(cfg.shared_intermediate, 64))
     from ironmlx_b200.workloads import Workload
     wl = Workload(wl_cfg)
@@ -65,7 +72,7 @@ def test_route_matches_checker(cuda, cfg):
                     num_experts_per_tok=cfg.top_k, norm_topk_prob=cfg.norm_topk_prob)
     if cfg.shared_intermediate:
         p.shared_expert_gate_w = wl.shared_gate_weight().astype(F.bf16)
-    idx, w, sg, x16 = run_route(x, p, cfg.top_k, cfg.norm_topk_prob, cuda)
+    idx, w, sg, x16 = run_route(x, p, cfg.top_k, cfg.norm_topk_prob, cuda, ws=ws)
     check_routing(idx, w, x, p, cfg.top_k, cfg.norm_topk_prob)
     # the fp16 copy is exact except below fp16's subnormal spacing (2^-24)
     big = np.abs(x) >= 2.0 ** -14
@@ -77,19 +84,20 @@ def test_route_matches_checker(cuda, cfg):
         assert np.allclose(sg, ref, rtol=1e-5, atol=1e-6)
 
 
-def test_route_with_logit_bias_and_exact_ties(cuda):
+@pytest.mark.parametrize("ws", [False, True], ids=["plain", "scratch"])
+def test_route_with_logit_bias_and_exact_ties(cuda, ws):
     cfg = MoEConfig("b", 33, 256, 64, 8, 64, 0, seed=8)
     from ironmlx_b200.workloads import Workload
     wl = Workload(cfg)
     x = wl.activations()
     p = O.MoEParams(router_w=wl.router_weight().astype(F.bf16), gate_up=None, down=None, num_experts_per_tok=8)
     bias = np.linspace(-2, 0, 64).astype(np.float32)
-    idx, w, _, _ = run_route(x, p, 8, True, cuda, bias)
+    idx, w, _, _ = run_route(x, p, 8, True, cuda, bias, ws=ws)
     check_routing(idx, w, x, p, 8, True, bias)
     # exact ties: all-zero router -> equal probabilities -> experts 0..k-1 in order
     p0 = O.MoEParams(router_w=np.zeros((64, 256), np.float32).astype(F.bf16), gate_up=None, down=None,
                      num_experts_per_tok=8)
-    idx, w, _, _ = run_route(x, p0, 8, True, cuda)
+    idx, w, _, _ = run_route(x, p0, 8, True, cuda, ws=ws)
     assert np.array_equal(idx, np.tile(np.arange(8, dtype=np.int32), (33, 1))) and np.allclose(w, 0.125)
 
 
