@@ -208,38 +208,7 @@ int run_experts(int path, const GroupedArgs& ga, cudaStream_t stream, cudaEvent_
     return launch_generic_grouped(ga, stream, mid);
 }
 
-__global__ void build_units_kernel(const int32_t* __restrict__ offsets, int E, int unit_rows,
-                                   WorkUnit* __restrict__ units, int32_t* __restrict__ n_units,
-                                   int32_t* __restrict__ sched) {
-    // one thread per expert is plenty here: sequential emission keeps the list in expert order
-    if (threadIdx.x == 0) {
-        int n = 0;
-        for (int e = 0; e < E; ++e) {
-            const int lo = offsets[e], cnt = offsets[e + 1] - lo;
-            for (int c = 0; c * unit_rows < cnt; ++c) {
-                WorkUnit u;
-                u.expert = e;
-                u.slot0 = lo + c * unit_rows;
-                u.rows = min(unit_rows, cnt - c * unit_rows);
-                u.pad = 0;
-                units[n++] = u;
-            }
-        }
-        n_units[0] = n;
-        n_units[1] = n;          // no extra expert at this entry point: all units are routed
-    }
-    if (sched != nullptr)
-        for (int i = threadIdx.x; i < kSchedInts; i += blockDim.x) sched[i] = 0;
-}
-
 }  // namespace
-
-int launch_build_units(const int32_t* offsets, int E, int unit_rows, WorkUnit* units, int32_t* n_units,
-                       int32_t* sched, cudaStream_t stream) {
-    build_units_kernel<<<1, 256, 0, stream>>>(offsets, E, unit_rows, units, n_units, sched);
-    IMX_CHECK_CUDA(cudaGetLastError());
-    return IMX_OK;
-}
 
 namespace {
 struct ExpertsWs {
@@ -271,8 +240,10 @@ ExpertsWs carve_experts(const imx_moe_config& c, int n_rows, int n_src_rows, voi
 }
 
 __global__ void permute_rows_kernel(const __half* __restrict__ src, const int32_t* __restrict__ row_index,
-                                    int H, __half* __restrict__ dst, const Order16 order) {
+                                    int H, __half* __restrict__ dst, const Order16 order,
+                                    const int32_t* __restrict__ n_rows_dev) {
     const int r = blockIdx.x;
+    if (n_rows_dev != nullptr && r >= *n_rows_dev) return;      // rows past the last sorted slot are nobody's
     const __half* s = src + (size_t)(row_index ? row_index[r] : r) * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         const __half v = s[(i & ~15) + order.o[i & 15]];
@@ -574,7 +545,8 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
         Order16 order;
         for (int i = 0; i < 16; ++i) order.o[i] = (int8_t)o[i];
         order.pair_scale_odd = path == IMX_PATH_DECODE && decode_tmap_supported(set) ? 0.0625f : 1.f;
-        permute_rows_kernel<<<n_rows, 256, 0, stream>>>((const __half*)x_f16, row_index, c.hidden, ws.xperm, order);
+        permute_rows_kernel<<<n_rows, 256, 0, stream>>>((const __half*)x_f16, row_index, c.hidden, ws.xperm, order,
+                                                        offsets + num_experts);
         IMX_CHECK_CUDA(cudaGetLastError());
         ga.in = ws.xperm;
         ga.row_index = nullptr;
@@ -587,6 +559,7 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
     ga.gsum = ws.gsum;
     ga.gsum_x = ws.gsum_x;
     ga.n_in_rows = n_rows;
+    ga.n_rows_dev = offsets + num_experts;
     ga.gsum_x_ready = 0;
     ga.act = ws.act;
     ga.act_stride = c.intermediate;

@@ -132,9 +132,9 @@ struct Cursor {
 // out[slot, j] = 2^-24 * sum(x[row(slot), 64 j .. 64 j + 63]), fixed order, fp32.  The rows are in the
 // expert kernels' layout: pairs 1 and 3 of every 8 stored values hold x / 16.
 __global__ void group_sums_kernel(const __half* __restrict__ in, const int32_t* __restrict__ row_index, int n_slots,
-                                  int groups, int ld, float* __restrict__ out) {
+                                  int groups, int ld, float* __restrict__ out, const int32_t* __restrict__ n_rows_dev) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= n_slots * groups) return;
+    if (idx >= (n_rows_dev != nullptr ? min(n_slots, *n_rows_dev) : n_slots) * groups) return;
     const int slot = idx / groups, j = idx - slot * groups;
     const int row = row_index ? row_index[slot] : slot;
     const uint4* p = reinterpret_cast<const uint4*>(in + (size_t)row * ld + (size_t)j * 64);
@@ -571,7 +571,8 @@ int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn
     const int g_in = s.n_in / 64, g_mid = mid_max / 64;
     if (!a.gsum_x_ready) {
         const int n = a.n_in_rows * g_in;
-        group_sums_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a.in, nullptr, a.n_in_rows, g_in, s.n_in, a.gsum_x);
+        group_sums_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a.in, nullptr, a.n_in_rows, g_in, s.n_in, a.gsum_x,
+                                                             a.n_rows_dev);
         IMX_CHECK_CUDA(cudaGetLastError());
     }
     decode_tmap_kernel<true, kWarps, kStages><<<grid, kWarps * 32, smem_gu, stream>>>(

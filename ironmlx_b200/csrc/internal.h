@@ -107,6 +107,7 @@ struct GroupedArgs {
     float* gsum;                   // [n_slots, act_stride / 64] fp32 group sums of the SwiGLU rows (tensor-map decode kernel)
     float* gsum_x;                 // [n_in_rows, n_in / 64] fp32 group sums of the rows of `in`
     int n_in_rows;                 // rows of `in`
+    const int32_t* n_rows_dev;     // device-side count of rows of `in` that are in use (nullptr: all n_in_rows)
     int gsum_x_ready;              // the router already filled gsum_x
     __half* act;                   // fp16 [n_slots, act_stride]
     int act_stride;

@@ -215,9 +215,11 @@ sort_fused_kernel(const int32_t* __restrict__ ids, int A, int E, int32_t* __rest
     emit_aux(aux, perm, s_off, E, A, s_warp);
 }
 
-// One block, at most one id per thread (A <= kSortThreads, E <= kSmallSortExperts): ids are read
-// once, ranks stay in registers, and every output is written once (decode-size batches).
+// One block, at most kSmallSortIters ids per thread (A <= kSmallSortIters * kSortThreads, E <=
+// kSmallSortExperts): ids are read once, ranks stay in registers, and every output is written once
+// (decode-size batches).  A warp owns a contiguous run of ids, so ranks follow the index order.
 constexpr int kSmallSortExperts = 256;
+constexpr int kSmallSortIters = 4;
 
 __global__ void __launch_bounds__(kSortThreads)
 sort_small_kernel(const int32_t* __restrict__ ids, int A, int E, int32_t* __restrict__ counts,
@@ -229,20 +231,43 @@ sort_small_kernel(const int32_t* __restrict__ ids, int A, int E, int32_t* __rest
     int* s_off = s_tot + E;                    // [E+1]
     int* s_warp = s_off + E + 1;               // [33]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    int e = tid < A ? ids[tid] : -1;
-    if (e < 0 || e >= E) e = -1;                          // moe.rs:100: out-of-range ids are dropped
-    const float w = (tid < A && aux.topk_w != nullptr) ? aux.topk_w[tid] : 1.f;
-    const int n_warps = (A + 31) >> 5;
-    for (int i = tid; i < n_warps * E; i += kSortThreads) s_hist[i] = 0;
+    const int per_warp = ((A + kSortWarps - 1) / kSortWarps + 31) & ~31;      // <= 32 * kSmallSortIters
+    const int w_lo = warp * per_warp, w_hi = min(A, w_lo + per_warp);
+    int e[kSmallSortIters], rank[kSmallSortIters];
+    float w[kSmallSortIters];
+#pragma unroll
+    for (int it = 0; it < kSmallSortIters; ++it) {
+        const int i = w_lo + it * 32 + lane;
+        const bool in = it * 32 < per_warp && i < w_hi;
+        int v = in ? ids[i] : -1;
+        if (v < 0 || v >= E) v = -1;                      // moe.rs:100: out-of-range ids are dropped
+        e[it] = v;
+        w[it] = (in && aux.topk_w != nullptr) ? aux.topk_w[i] : 1.f;
+        rank[it] = 0;
+    }
+    for (int i = tid; i < kSortWarps * E; i += kSortThreads) s_hist[i] = 0;
     __syncthreads();
-    // rank among equal ids inside the warp; the first lane of every group leaves the group's size
-    const unsigned peers = __match_any_sync(0xffffffffu, e);
-    int rank = __popc(peers & ((1u << lane) - 1u));
-    if (e >= 0 && rank == 0) s_hist[warp * E + e] = __popc(peers);
+    int* my_hist = s_hist + warp * E;
+    const unsigned lt = (1u << lane) - 1u;
+#pragma unroll
+    for (int it = 0; it < kSmallSortIters; ++it) {
+        if (it * 32 < per_warp) {
+            // rank among equal ids: those of earlier passes of the warp, then lower lanes of this pass
+            const unsigned peers = __match_any_sync(0xffffffffu, e[it]);
+            const int before = e[it] >= 0 ? my_hist[e[it]] : 0;
+            __syncwarp();
+            if (e[it] >= 0) {
+                const int r = __popc(peers & lt);
+                if (r == 0) my_hist[e[it]] = before + __popc(peers);
+                rank[it] = before + r;
+            }
+            __syncwarp();
+        }
+    }
     __syncthreads();
     for (int x = tid; x < E; x += kSortThreads) {          // exclusive scan over warps, per expert
         int run = 0;
-        for (int v = 0; v < n_warps; ++v) {
+        for (int v = 0; v < kSortWarps; ++v) {
             const int c = s_hist[v * E + x];
             s_hist[v * E + x] = run;
             run += c;
@@ -251,19 +276,25 @@ sort_small_kernel(const int32_t* __restrict__ ids, int A, int E, int32_t* __rest
         if (counts != nullptr) counts[x] = run;
     }
     __syncthreads();
-    if (e >= 0) rank += s_hist[warp * E + e];
+#pragma unroll
+    for (int it = 0; it < kSmallSortIters; ++it)
+        if (e[it] >= 0) rank[it] += my_hist[e[it]];
     scan_experts(s_tot, E, offsets, s_off, s_warp);
-    if (tid < A) {
-        if (e >= 0) {
-            const int pos = s_off[e] + rank;
-            perm[pos] = tid;
-            inv_perm[tid] = pos;
-            if (aux.tok_of_slot != nullptr) {
-                aux.tok_of_slot[pos] = tid / aux.top_k;
-                if (aux.w_of_slot) aux.w_of_slot[pos] = w;
+#pragma unroll
+    for (int it = 0; it < kSmallSortIters; ++it) {
+        const int i = w_lo + it * 32 + lane;
+        if (it * 32 < per_warp && i < w_hi) {
+            if (e[it] >= 0) {
+                const int pos = s_off[e[it]] + rank[it];
+                perm[pos] = i;
+                inv_perm[i] = pos;
+                if (aux.tok_of_slot != nullptr) {
+                    aux.tok_of_slot[pos] = i / aux.top_k;
+                    if (aux.w_of_slot) aux.w_of_slot[pos] = w[it];
+                }
+            } else {
+                inv_perm[i] = -1;
             }
-        } else {
-            inv_perm[tid] = -1;
         }
     }
     if (aux.tok_of_slot != nullptr && aux.shared_gate != nullptr) {
@@ -347,6 +378,45 @@ sort_place_kernel(const int32_t* __restrict__ ids, int A, int E, const int32_t* 
 
 }  // namespace
 
+// Unit list for a caller-given offsets array (stage-level API): one thread per expert, a block scan for
+// the positions; also clears the scheduler words.
+static __global__ void __launch_bounds__(kSortThreads)
+build_units_kernel(const int32_t* __restrict__ offsets, int E, int unit_rows, WorkUnit* __restrict__ units,
+                   int32_t* __restrict__ n_units, int32_t* __restrict__ sched) {
+    __shared__ int s_warp[33];
+    const int tid = threadIdx.x;
+    int cnt = 0, pos0 = 0;
+    if (tid < E) {
+        pos0 = offsets[tid];
+        cnt = offsets[tid + 1] - pos0;
+    }
+    const int nu = (cnt + unit_rows - 1) / unit_rows;
+    int total;
+    const int base = block_exclusive_scan(nu, s_warp, &total);
+    for (int c = 0; c < nu; ++c) {
+        WorkUnit u;
+        u.expert = tid;
+        u.slot0 = pos0 + c * unit_rows;
+        u.rows = min(unit_rows, cnt - c * unit_rows);
+        u.pad = 0;
+        units[base + c] = u;
+    }
+    if (tid == 0) {
+        n_units[0] = total;
+        n_units[1] = total;          // no extra expert at this entry point: all units are routed
+    }
+    if (sched != nullptr)
+        for (int i = tid; i < kSchedInts; i += kSortThreads) sched[i] = 0;
+}
+
+int launch_build_units(const int32_t* offsets, int E, int unit_rows, WorkUnit* units, int32_t* n_units,
+                       int32_t* sched, cudaStream_t stream) {
+    IMX_REQUIRE(E >= 1 && E < kSortThreads, "build_units: num_experts (%d) must be in 1..%d", E, kSortThreads - 1);
+    build_units_kernel<<<1, kSortThreads, 0, stream>>>(offsets, E, unit_rows, units, n_units, sched);
+    IMX_CHECK_CUDA(cudaGetLastError());
+    return IMX_OK;
+}
+
 // ── allocation-free variant ─────────────────────────────────────────────────
 // Scratch of the multi-block path for callers that cannot provide any: a fixed
 // array that lives in the library's device image (every GPU that loads the
@@ -408,7 +478,7 @@ int launch_sort(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offs
         IMX_REQUIRE(aux.units == nullptr || E + 1 <= kSortThreads, "sort: too many experts for the unit list");
     }
     const size_t smem_fused = ((size_t)kSortWarps * E + E + E + 1 + 33) * sizeof(int);
-    if (A <= kSortThreads && E <= kSmallSortExperts) {
+    if (A <= kSmallSortIters * kSortThreads && E <= kSmallSortExperts) {
         sort_small_kernel<<<1, kSortThreads, smem_fused, stream>>>(ids, A, E, counts, offsets, perm, inv_perm, aux);
         IMX_CHECK_CUDA(cudaGetLastError());
         return IMX_OK;
