@@ -280,7 +280,8 @@ def main():
     if runner is None:
         xh = x.cpu().pin_memory()
         yh = torch.empty_like(xh).pin_memory()
-        e2e_step = lambda: moe.forward_host(xh, yh)
+        captured_host = moe.capture(x, xh, yh)   # copy in, block, copy out as one graph; sync per step
+        e2e_step = captured_host.run_host
     else:
         e2e_step = runner.step_host
     for _ in range(3):

@@ -36,6 +36,8 @@
 // Every copy is issued per CTA; the kernel uses no thread-block clusters.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "decode_common.cuh"
 
 namespace imx {
@@ -44,15 +46,12 @@ namespace {
 
 using namespace decode;
 
-constexpr int kThreads = 512;
 constexpr int kStages = 5;
 constexpr int kTileM = 128, kTileN = 128, kTileK = 64;
 constexpr int kABytes = kTileM * kTileK * 2;      // 16 KB
 constexpr int kBBytes = kTileN * kTileK * 2;      // 16 KB
 constexpr int kQBytes = kTileN * kTileK / 2;       // 4 KB of packed 4-bit codes (128 rows x 32 bytes)
 constexpr int kStageBytes = kABytes + kBBytes + kQBytes;   // 36 KB: A (fp16) | B (fp16, dequantized) | Q (packed)
-constexpr int kProducerWarps = 8;
-constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kSpin = 1 << 22;
 constexpr uint32_t kTmemCols = 256;               // two 128-column fp32 accumulators
 
@@ -209,8 +208,10 @@ __device__ __forceinline__ __half2 bf16_to_half2(uint16_t b) {
     return __float2half2_rn(__uint_as_float((uint32_t)b << 16));
 }
 
-template <bool SWIGLU, bool G128>
-__global__ void __launch_bounds__(kThreads, 1)
+// PW producer warps in PW / 4 groups (a group of four warps dequantizes one stage; group j takes the K
+// steps j, j + PW/4, ...); the block has 8 + PW warps.
+template <bool SWIGLU, bool G128, int PW>
+__global__ void __launch_bounds__(256 + 32 * PW, 1)
 prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const int srow_max,
                     const __grid_constant__ PrefillMaps maps) {
     extern __shared__ unsigned char smem_raw[];
@@ -229,14 +230,14 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const i
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&bars->qfull[s]), 1);
-            mbar_init(smem_u32(&bars->full[s]), kProducerWarps / 2);
+            mbar_init(smem_u32(&bars->full[s]), 4);
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bars->acc_full[b]), 1);
             mbar_init(smem_u32(&bars->acc_empty[b]), 4);
             mbar_init(smem_u32(&bars->sfull[b]), 1);
-            mbar_init(smem_u32(&bars->sempty[b]), kProducerWarps);
+            mbar_init(smem_u32(&bars->sempty[b]), PW);
         }
         bars->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -397,8 +398,8 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const i
         }
     } else if (warp >= 8) {
         // ── producers ───────────────────────────────────────────────────────
-        // Two groups of four warps: group 0 fills the even K steps, group 1 the odd
-        // ones, so two stages are always being produced at once.  Inside a group a
+        // PW / 4 groups of four warps: group j fills the K steps j, j + PW / 4, ..., so PW / 4
+        // stages are being produced at once.  Inside a group a
         // thread owns one weight row of the tile: 32 bytes of packed codes per K step
         // (prefetched one of its own steps ahead), dequantized into eight 16-byte chunks.
         const int grp_id = (warp - 8) >> 2;
@@ -420,7 +421,7 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const i
             uint4 sv = make_uint4(0, 0, 0, 0), bv = make_uint4(0, 0, 0, 0);   // eight groups' scales / biases
             int cur_blk = -1;
             bool ok = true;
-            for (int ks = grp_id; ks < ksteps; ks += 2) {
+            for (int ks = grp_id; ks < ksteps; ks += PW / 4) {
                 const int n = n_tile0 + ks;
                 const int s = n % kStages;
                 const int gi = G128 ? (ks >> 1) : ks;     // group of this K step
@@ -558,11 +559,6 @@ int launch_prefill_umma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t m
         int dev = 0, v = 0;
         IMX_CHECK_CUDA(cudaGetDevice(&dev));
         IMX_CHECK_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
-        const int big = 227 * 1024;
-        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-        IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
         sms = v;
     }
     // activations in sorted-slot order (the `take_axis` of moe.rs:124-127, once for all experts)
@@ -589,14 +585,28 @@ int launch_prefill_umma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t m
     }
     if (!s.has_extra) { gu.w[2] = gu.w[0]; gu.s[2] = gu.s[0]; gu.b[2] = gu.b[0]; }
     dn.w[2] = dn.w[0]; dn.s[2] = dn.s[0]; dn.b[2] = dn.b[0];
-    auto k_gu = g128 ? prefill_umma_kernel<true, true> : prefill_umma_kernel<true, false>;
-    auto k_dn = g128 ? prefill_umma_kernel<false, true> : prefill_umma_kernel<false, false>;
-    k_gu<<<sms, kThreads, smem_for(srow_gu), stream>>>(a, s.n_mid / 64, x_mid / 64, srow_gu, gu);
-    IMX_CHECK_CUDA(cudaGetLastError());
-    if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
-    k_dn<<<sms, kThreads, smem_for(srow_dn), stream>>>(a, s.n_in / 128, s.n_in / 128, srow_dn, dn);
-    IMX_CHECK_CUDA(cudaGetLastError());
-    return IMX_OK;
+    const size_t smem_gu = smem_for(srow_gu), smem_dn = smem_for(srow_dn);
+    auto run = [&](auto pw_tag) -> int {
+        constexpr int PW = decltype(pw_tag)::value;
+        auto k_gu = g128 ? prefill_umma_kernel<true, true, PW> : prefill_umma_kernel<true, false, PW>;
+        auto k_dn = g128 ? prefill_umma_kernel<false, true, PW> : prefill_umma_kernel<false, false, PW>;
+        static bool configured = false;      // once per instantiation, outside any stream capture (first call)
+        if (!configured) {
+            IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<true, true, PW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<true, false, PW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<false, true, PW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<false, false, PW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            configured = true;
+        }
+        k_gu<<<sms, 256 + 32 * PW, smem_gu, stream>>>(a, s.n_mid / 64, x_mid / 64, srow_gu, gu);
+        IMX_CHECK_CUDA(cudaGetLastError());
+        if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
+        k_dn<<<sms, 256 + 32 * PW, smem_dn, stream>>>(a, s.n_in / 128, s.n_in / 128, srow_dn, dn);
+        IMX_CHECK_CUDA(cudaGetLastError());
+        return IMX_OK;
+    };
+    // 8 producer warps: 12 and 16 measured the same (the producers are not what the MMAs wait for)
+    return run(std::integral_constant<int, 8>{});
 }
 
 }  // namespace imx

@@ -189,11 +189,14 @@ class MoEMLP:
                                     ws.numel(), ops.stream_ptr(stream), None if tr is None else C.byref(tr)))
         return (y, tensors) if trace else y
 
-    def capture(self, x: torch.Tensor) -> "CapturedForward":
+    def capture(self, x: torch.Tensor, x_host: Optional[torch.Tensor] = None,
+                y_host: Optional[torch.Tensor] = None) -> "CapturedForward":
         """The block for a fixed input buffer as a CUDA graph: every kernel of
         `forward_with_stream(x)` recorded once and replayed with one launch
-        (decode loops call the block with the same shapes every step)."""
-        return CapturedForward(self, x)
+        (decode loops call the block with the same shapes every step).  With
+        pinned host buffers the graph also holds the copy of `x_host` to the
+        device before the block and the copy of the result to `y_host` after it."""
+        return CapturedForward(self, x, x_host, y_host)
 
     def forward_timed(self, x: torch.Tensor, stream=None):
         """-> (y, [router, sort, gate/up, down, combine] milliseconds), measured
@@ -230,9 +233,14 @@ class CapturedForward:
     copies), call, read `y`.  The graph holds the block's workspace, so one
     instance serves one stream of steps at a time."""
 
-    def __init__(self, moe: "MoEMLP", x: torch.Tensor):
+    def __init__(self, moe: "MoEMLP", x: torch.Tensor, x_host: Optional[torch.Tensor] = None,
+                 y_host: Optional[torch.Tensor] = None):
         self.moe = moe
         self.x = x.contiguous().clone()
+        self.x_host, self.y_host = x_host, y_host
+        for h in (x_host, y_host):
+            if h is not None and not h.is_pinned():
+                raise IronMLXError(_lib.ERR_INVALID, "capture: host buffers must be pinned memory")
         side = torch.cuda.Stream(device=x.device)
         side.wait_stream(torch.cuda.current_stream(x.device))
         with torch.cuda.stream(side):                    # warm up off the capture: attributes, workspace
@@ -242,13 +250,25 @@ class CapturedForward:
         torch.cuda.synchronize(x.device)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
+            if x_host is not None:
+                self.x.copy_(x_host.view_as(self.x), non_blocking=True)
             self.y = moe.forward_with_stream(self.x)
+            if y_host is not None:
+                y_host.view_as(self.y).copy_(self.y, non_blocking=True)
 
     def __call__(self, x: Optional[torch.Tensor] = None) -> torch.Tensor:
         if x is not None and x.data_ptr() != self.x.data_ptr():
             self.x.copy_(x, non_blocking=True)
         self.graph.replay()
         return self.y
+
+    def run_host(self) -> torch.Tensor:
+        """Host buffers in, host buffers out: one replay (copy in, block, copy out) and a stream sync."""
+        if self.x_host is None or self.y_host is None:
+            raise IronMLXError(_lib.ERR_INVALID, "capture: no host buffers were given")
+        self.graph.replay()
+        torch.cuda.current_stream(self.x.device).synchronize()
+        return self.y_host
 
 
 @dataclass
