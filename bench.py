@@ -330,11 +330,11 @@ def main():
             achieved = gu_bytes / (stage[2] * 1e-3) / 1e9
             total_bytes = algorithmic_bytes_decode(cfg, touched)
             line["roofline"] = {
-                "bound": "hbm", "kernel": "decode_tma_kernel<true> (gate/up + SwiGLU)", "achieved": achieved,
+                "bound": "hbm", "kernel": "decode_tmap_kernel<true> (gate/up + SwiGLU)", "achieved": achieved,
                 "peak": peak, "peak_source": f"of {which}", "unit": "GB/s", "frac": achieved / peak,
-                "traffic": 257.1e6 if cfg.name == "c2" else None,
+                "traffic": 265.1e6 if cfg.name == "c2" else None,
                 "traffic_note": "dram read+write per launch from the ncu capture of a 97-expert case, scaled by touched experts "
-                                "(profiles/decode_tma_kernel_c2.md); equals the algorithmic bytes",
+                                "(profiles/decode_tmap_kernel_c2.md): the algorithmic bytes plus the SwiGLU rows written",
                 "algorithmic_bytes_per_launch": gu_bytes, "launch_ms": float(stage[2]), "stage_ms": stage_ms,
                 "layer": {"algorithmic_bytes": total_bytes, "touched_experts": touched,
                           "achieved_gbs": total_bytes / (ms * 1e-3) / 1e9, "frac": total_bytes / (ms * 1e-3) / 1e9 / peak},
