@@ -131,6 +131,22 @@ IMX_API int imx_moe_forward(const imx_moe_config* cfg, const imx_moe_weights* w,
                     int n_tokens, void* y, void* workspace, size_t workspace_bytes,
                     void* stream, const imx_moe_trace* trace);
 
+/* The MoE half of a decoder layer, mlx/src/model/qwen35.rs:271-276:
+ *   y = h + MoE(rms_norm(h, ln_weight, eps))
+ * with the normalisation applied where the router loads h and the residual added
+ * where the combine stage rounds its sums, so neither the normalised activations
+ * nor the block output make a round trip through memory on their own.
+ * h, y: bf16 [N, H]; ln_weight: bf16 [H] or NULL (rms_norm without weight,
+ * mlx/src/fast.rs:37-49).  Same workspace as imx_moe_forward. */
+IMX_API int imx_moe_forward_residual(const imx_moe_config* cfg, const imx_moe_weights* w, const void* h,
+                             const void* ln_weight, float eps, int n_tokens, void* y, void* workspace,
+                             size_t workspace_bytes, void* stream, const imx_moe_trace* trace);
+
+/* y[n_rows, hidden] = rms_norm(x, weight, eps) (mlx/src/nn/norm.rs:21-24 ->
+ * fast::rms_norm, mlx/src/fast.rs:37-49); bf16 in and out, weight bf16 [hidden] or NULL. */
+IMX_API int imx_rms_norm(const void* x, int n_rows, int hidden, const void* weight, float eps, void* y,
+                 void* stream);
+
 /* imx_moe_forward with CUDA events recorded on the stream between its stages;
  * synchronises and returns the five stage durations in milliseconds:
  * router, dispatch sort, first expert product (gate/up + SwiGLU), second

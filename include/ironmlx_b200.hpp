@@ -7,6 +7,7 @@
 //   Error / check               mlx/src/error.rs:17-54 (message of the failed call)
 //   Linear                      mlx/src/nn/linear.rs:150-177 (dense, bf16)
 //   QuantizedLinear             mlx/src/nn/linear.rs:13-63 (new, new_with_mode, forward_with_stream)
+//   RMSNorm                     mlx/src/nn/norm.rs:11-24 (weight, eps, forward_with_stream -> fast::rms_norm)
 //   MLP / Expert                mlx/src/nn/mlp.rs:12-33, mlx/src/nn/moe.rs:11-33
 //   MoEMLP                      mlx/src/nn/moe.rs:39-183 (gate, experts, shared_expert,
 //                               shared_expert_gate, num_experts_per_tok, norm_topk_prob,
@@ -144,6 +145,16 @@ struct QuantizedLinear {
     }
 };
 
+struct RMSNorm {
+    Array weight;   // [H] bf16
+    float eps = 1e-6f;
+    RMSNorm(Array w, float e) : weight(std::move(w)), eps(e) {}
+    void forward_with_stream(const Array& x, Array& y, cudaStream_t stream = nullptr) const {
+        const int h = (int)x.dim(-1);
+        check(imx_rms_norm(x.ptr, (int)(x.size() / h), h, weight.ptr, eps, y.ptr, stream));
+    }
+};
+
 // SwiGLU MLP: down(silu(gate(x)) * up(x)); the shared expert of the block.
 struct MLP {
     QuantizedLinear gate_proj, up_proj, down_proj;
@@ -213,6 +224,19 @@ public:
         const imx_moe_weights w = weights();
         ensure_workspace(c, n);
         check(imx_moe_forward(&c, &w, x.ptr, n, y.ptr, workspace_, workspace_bytes_, stream, nullptr));
+    }
+
+    // The MoE half of a decoder layer (mlx/src/model/qwen35.rs:271-276): y = h + forward(norm.forward(h)),
+    // with the normalisation and the residual add fused into the block's first and last kernels.
+    void forward_residual(const Array& h, const RMSNorm& norm, Array& y, cudaStream_t stream = nullptr) {
+        const imx_moe_config c = config();
+        if (h.dtype != Dtype::Bfloat16 || y.dtype != Dtype::Bfloat16 || h.dim(-1) != c.hidden || y.size() != h.size())
+            throw Error(IMX_ERR_INVALID, "MoEMLP: h and y must be bfloat16 arrays [.., hidden] of equal size");
+        const int n = (int)(h.size() / c.hidden);
+        const imx_moe_weights w = weights();
+        ensure_workspace(c, n);
+        check(imx_moe_forward_residual(&c, &w, h.ptr, norm.weight.ptr, norm.eps, n, y.ptr, workspace_, workspace_bytes_,
+                                       stream, nullptr));
     }
 
     // Device status word of the block's kernels (bounded waits that expired); throws if it is set.

@@ -47,6 +47,9 @@ SIGNATURES = {
     "imx_moe_workspace_bytes": (_i, [C.POINTER(MoEConfig), _i, C.POINTER(_sz)]),
     "imx_moe_forward": (_i, [C.POINTER(MoEConfig), C.POINTER(MoEWeights), _vp, _i, _vp, _vp, _sz, _vp,
                              C.POINTER(MoETrace)]),
+    "imx_moe_forward_residual": (_i, [C.POINTER(MoEConfig), C.POINTER(MoEWeights), _vp, _vp, _f, _i, _vp, _vp, _sz, _vp,
+                                      C.POINTER(MoETrace)]),
+    "imx_rms_norm": (_i, [_vp, _i, _i, _vp, _f, _vp, _vp]),
     "imx_moe_forward_timed": (_i, [C.POINTER(MoEConfig), C.POINTER(MoEWeights), _vp, _i, _vp, _vp, _sz, _vp,
                                    C.POINTER(C.c_float)]),
     "imx_moe_forward_host": (_i, [C.POINTER(MoEConfig), C.POINTER(MoEWeights), _vp, _i, _vp, _vp, _sz, _vp]),

@@ -42,6 +42,8 @@ struct ForwardWs {
     float* partials;      // [kFlagWarps][256] hand-off slots of the decode kernels
     float* gsum;          // [A + N, act_stride / 64] group sums of the SwiGLU rows (decode kernels)
     float* gsum_x;        // [N, H / 64] group sums of the fp16 copy of x
+    float* inv_rms;          // [N] RMSNorm factor per token (decoder-layer tail)
+    __nv_bfloat16* xn;       // [N, H] normalised input where the router cannot normalise its own tiles
     float* route_partials;   // split-K router: [splits][32 ceil(N / 32)][E]
     float* route_sg;         // split-K router: [splits][32 ceil(N / 32)]
     int32_t* topk_idx;    // [A]
@@ -98,6 +100,8 @@ ForwardWs carve_forward(const imx_moe_config& c, int n, void* base) {
     w.rows = cv.take<float>((size_t)(A + ns) * c.hidden);
     w.gsum = cv.take<float>((size_t)(A + ns) * (w.act_stride / 64 + 1));
     w.gsum_x = cv.take<float>((size_t)n * (c.hidden / 64 + 1));
+    w.inv_rms = cv.take<float>((size_t)n);
+    w.xn = cv.take<__nv_bfloat16>((size_t)n * c.hidden);
     const int slice = route_slice(c.hidden);
     if (n < kRouteSplitMaxTokens && slice > 0) {
         const size_t splits = (size_t)c.hidden / slice, n_pad = (size_t)(n + 31) / 32 * 32;
@@ -289,9 +293,15 @@ int imx_moe_workspace_bytes(const imx_moe_config* cfg, int n_tokens, size_t* byt
     return IMX_OK;
 }
 
+// The glue of the decoder layer around the block (qwen35.rs:271-276), when asked for.
+struct LayerTail {
+    const void* ln_weight;   // RMSNorm weight (bf16 [H]) or nullptr
+    float eps;
+};
+
 static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, const void* x, int n_tokens,
                         void* y, void* workspace, size_t workspace_bytes, void* stream_,
-                        const imx_moe_trace* trace, cudaEvent_t* ev) {
+                        const imx_moe_trace* trace, cudaEvent_t* ev, const LayerTail* tail = nullptr) {
     QFormat f;
     IMX_TRY(check_config(cfg, &f));
     IMX_REQUIRE(w != nullptr && w->router_w != nullptr, "forward: router weight is required");
@@ -322,10 +332,24 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     decode_block_order(path != IMX_PATH_GENERIC ? f.bits : 0, order);
     auto mark = [&](int i) -> cudaError_t { return ev ? cudaEventRecord(ev[i], stream) : cudaSuccess; };
     const bool tmap_decode = path == IMX_PATH_DECODE && decode_tmap_supported(set);
-    RouteScratch rscratch = {ws.route_partials, ws.route_sg, tmap_decode ? ws.gsum_x : nullptr};
+    RouteScratch rscratch = {ws.route_partials, ws.route_sg, tmap_decode ? ws.gsum_x : nullptr, nullptr, nullptr};
     bool sums_done = false;
     IMX_CHECK_CUDA(mark(0));
-    IMX_TRY(launch_route(x, n_tokens, c.hidden, w->router_w, w->router_logit_bias, c.num_experts, c.top_k,
+    const void* router_in = x;
+    if (tail != nullptr) {
+        // y = x + MoE(rms_norm(x)): the split-K router normalises its tiles itself from the per-token factor;
+        // the other routers read a normalised copy
+        IMX_REQUIRE(tail->ln_weight == nullptr || ((uintptr_t)tail->ln_weight % 16) == 0, "forward: ln_weight must be 16-byte aligned");
+        const bool in_router = ws.route_partials != nullptr && c.num_experts % 32 == 0;
+        IMX_TRY(launch_rms_norm(x, n_tokens, c.hidden, tail->ln_weight, tail->eps, in_router ? nullptr : ws.xn, ws.inv_rms, stream));
+        if (in_router) {
+            rscratch.inv_rms = ws.inv_rms;
+            rscratch.ln_weight = tail->ln_weight;
+        } else {
+            router_in = ws.xn;
+        }
+    }
+    IMX_TRY(launch_route(router_in, n_tokens, c.hidden, w->router_w, w->router_logit_bias, c.num_experts, c.top_k,
                          c.norm_topk_prob, has_shared ? w->shared_expert_gate_w : nullptr, ws.topk_idx,
                          ws.topk_w, ws.shared_gate, ws.x16, order, stream,
                          tmap_decode ? 0.0625f : 1.f, ws.route_partials ? &rscratch : nullptr, &sums_done));
@@ -367,7 +391,8 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     IMX_TRY(run_experts(path, ga, stream, ev ? ev[3] : nullptr));
     IMX_CHECK_CUDA(mark(4));
     IMX_TRY(launch_combine(ws.rows, nullptr, ws.inv_perm, n_tokens, c.top_k, c.hidden,
-                           has_shared ? ws.rows + (size_t)A * c.hidden : nullptr, y, stream));
+                           has_shared ? ws.rows + (size_t)A * c.hidden : nullptr, y, stream, false,
+                           tail != nullptr ? x : nullptr));
     IMX_CHECK_CUDA(mark(5));
     if (trace != nullptr) {
         auto cp = [&](void* dst, const void* src, size_t bytes) -> cudaError_t {
@@ -388,6 +413,18 @@ int imx_moe_forward(const imx_moe_config* cfg, const imx_moe_weights* w, const v
                     void* y, void* workspace, size_t workspace_bytes, void* stream_,
                     const imx_moe_trace* trace) {
     return forward_impl(cfg, w, x, n_tokens, y, workspace, workspace_bytes, stream_, trace, nullptr);
+}
+
+int imx_moe_forward_residual(const imx_moe_config* cfg, const imx_moe_weights* w, const void* h, const void* ln_weight,
+                             float eps, int n_tokens, void* y, void* workspace, size_t workspace_bytes, void* stream_,
+                             const imx_moe_trace* trace) {
+    const LayerTail tail = {ln_weight, eps};
+    return forward_impl(cfg, w, h, n_tokens, y, workspace, workspace_bytes, stream_, trace, nullptr, &tail);
+}
+
+int imx_rms_norm(const void* x, int n_rows, int hidden, const void* weight, float eps, void* y, void* stream) {
+    IMX_REQUIRE(y != nullptr, "rms_norm: y is required");
+    return launch_rms_norm(x, n_rows, hidden, weight, eps, y, nullptr, (cudaStream_t)stream);
 }
 
 int imx_moe_forward_timed(const imx_moe_config* cfg, const imx_moe_weights* w, const void* x, int n_tokens,
@@ -474,7 +511,7 @@ int imx_moe_route_ws(const void* x, int n_tokens, int hidden, const void* router
     RouteWs ws = carve_route(n_tokens, hidden, num_experts, scratch);
     IMX_REQUIRE(ws.bytes == 0 || (scratch != nullptr && ((uintptr_t)scratch % 256) == 0 && scratch_bytes >= ws.bytes),
                 "route: scratch of %zu bytes (256-byte aligned) needed, %zu given", ws.bytes, scratch_bytes);
-    RouteScratch rs = {ws.partials, ws.sg, nullptr};
+    RouteScratch rs = {ws.partials, ws.sg, nullptr, nullptr, nullptr};
     return launch_route(x, n_tokens, hidden, router_w, logit_bias, num_experts, top_k, norm_topk_prob,
                         shared_gate_w, topk_idx, topk_w, shared_gate, x_f16, nullptr, (cudaStream_t)stream, 1.f,
                         ws.partials ? &rs : nullptr, nullptr);

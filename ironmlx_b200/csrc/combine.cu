@@ -20,7 +20,7 @@ template <bool F32_OUT>
 __global__ void __launch_bounds__(kCThreads)
 combine_kernel(const float* __restrict__ rows, const float* __restrict__ row_scale,
                const int32_t* __restrict__ inv_perm, int k, int H, const float* __restrict__ shared_rows,
-               void* __restrict__ y_out) {
+               void* __restrict__ y_out, const __nv_bfloat16* __restrict__ residual) {
     __shared__ int s_raw[kMaxK];
     __shared__ int s_slot[kMaxK];
     const int t = blockIdx.x;
@@ -67,6 +67,12 @@ combine_kernel(const float* __restrict__ rows, const float* __restrict__ row_sca
         const float4 v = __ldg(reinterpret_cast<const float4*>(shared_rows + (size_t)t * H + c));
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
+    if (residual != nullptr) {       // the layer's residual stream (qwen35.rs:276), added before the one rounding
+        const uint2 rv = __ldg(reinterpret_cast<const uint2*>(residual + (size_t)t * H + c));
+        const float2 r0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rv.x));
+        const float2 r1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rv.y));
+        acc.x += r0.x; acc.y += r0.y; acc.z += r1.x; acc.w += r1.y;
+    }
     if (F32_OUT) {           // partial sums of expert parallelism: summed across ranks before the rounding
         *reinterpret_cast<float4*>(reinterpret_cast<float*>(y_out) + (size_t)t * H + c) = acc;
         return;
@@ -110,13 +116,14 @@ int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t
 }
 
 int launch_combine(const float* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,
-                   const float* shared_rows, void* y, cudaStream_t stream, bool f32_out) {
+                   const float* shared_rows, void* y, cudaStream_t stream, bool f32_out, const void* residual) {
     IMX_REQUIRE(k >= 1 && k <= kMaxK, "combine: top_k (%d) must be in 1..%d", k, kMaxK);
     IMX_REQUIRE(H % 4 == 0, "combine: hidden (%d) must be a multiple of 4", H);
     if (n == 0) return IMX_OK;
     dim3 grid(n, ceil_div(H, kCCols));
-    if (f32_out) combine_kernel<true><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y);
-    else combine_kernel<false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y);
+    const __nv_bfloat16* res = (const __nv_bfloat16*)residual;
+    if (f32_out) combine_kernel<true><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res);
+    else combine_kernel<false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res);
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }

@@ -95,6 +95,12 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// One element of RMSNorm as the reference's kernels compute it: the normalised value is rounded to bf16,
+// then multiplied by the (bf16) weight and rounded again.
+__device__ __forceinline__ __nv_bfloat16 rms_norm_apply(__nv_bfloat16 x, float inv, __nv_bfloat16 w, bool has_w) {
+    const __nv_bfloat16 t = __float2bfloat16_rn(__bfloat162float(x) * inv);
+    return has_w ? __float2bfloat16_rn(__bfloat162float(w) * __bfloat162float(t)) : t;
+}
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
 // Saturating fp32 -> fp16 (the activations are carried in fp16 between the

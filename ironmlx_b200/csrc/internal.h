@@ -51,6 +51,8 @@ struct RouteScratch {
     float* partials;      // [H / route_slice(H)][32 ceil(n / 32)][E] partial logits
     float* sg_partials;   // [H / route_slice(H)][32 ceil(n / 32)] partial shared-gate dot products
     float* gsum_x;        // [n][H / 64] group sums of the fp16 copy in units of 2^-24, or nullptr
+    const float* inv_rms; // [n] per-token RMSNorm factor: the tiles of x are normalised as they are loaded (or nullptr)
+    const void* ln_weight;// bf16 [H] RMSNorm weight that goes with inv_rms (or nullptr)
 };
 constexpr int kRouteSplitMaxTokens = 1024;   // the split-K router serves batches below this
 int route_slice(int H);                      // K slice of the split-K router (0: not applicable)
@@ -135,8 +137,12 @@ int make_tensor_map_2d(const void* base, CUtensorMapDataType dt, size_t esize, s
                        bool promote256 = false);
 int launch_generic_grouped(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 
+// `residual` (bf16 [n, H] or nullptr) is added to the fp32 sums before the one rounding.
 int launch_combine(const float* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,
-                   const float* shared_rows, void* y, cudaStream_t stream, bool f32_out = false);
+                   const float* shared_rows, void* y, cudaStream_t stream, bool f32_out = false,
+                   const void* residual = nullptr);
+// y = w * T(x * rsqrt(mean(x^2) + eps)) per row (y may be null), inv_out[row] = the factor (may be null).
+int launch_rms_norm(const void* x, int n, int H, const void* w, float eps, void* y, float* inv_out, cudaStream_t stream);
 int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,
                        cudaStream_t stream);
 

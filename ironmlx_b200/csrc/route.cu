@@ -386,6 +386,17 @@ route_splitk_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, co
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
+    if (rs.inv_rms != nullptr) {
+        // the block's input is RMSNorm(x): normalise the tile in place (everything below reads the tile)
+        const __nv_bfloat16* lw = reinterpret_cast<const __nv_bfloat16*>(rs.ln_weight);
+        for (int c = tid; c < 32 * ks; c += kSkThreads) {
+            const int r = c / ks, col = c - r * ks;
+            const int tok = tok0 + r;
+            if (tok < n_tokens)
+                s_x[r * pad + col] = rms_norm_apply(s_x[r * pad + col], rs.inv_rms[tok], lw ? lw[k0 + col] : s_x[0], lw != nullptr);
+        }
+        __syncthreads();
+    }
 
     float acc[2][4];
 #pragma unroll

@@ -36,6 +36,20 @@ class Linear:
 
 
 @dataclass
+class RMSNorm:
+    """mlx/src/nn/norm.rs:11-24: weight [H] and eps; forward = `fast::rms_norm`."""
+    weight: torch.Tensor
+    eps: float = 1e-6
+
+    @classmethod
+    def new(cls, weight: torch.Tensor, eps: float) -> "RMSNorm":
+        return cls(weight, eps)
+
+    def forward_with_stream(self, x: torch.Tensor, stream=None) -> torch.Tensor:
+        return ops.rms_norm(x, self.weight, self.eps, stream)
+
+
+@dataclass
 class QuantizedLinear:
     """mlx/src/nn/linear.rs:13-63: packed weight + per-group scales/biases,
     forward = `quantized_matmul(x, w, scales, biases, transpose=true, ...)`."""
@@ -187,6 +201,34 @@ class MoEMLP:
             tr = MoETrace(**{name: t.data_ptr() for name, t in tensors.items()})
         check(lib().imx_moe_forward(C.byref(cfg), C.byref(w), x.data_ptr(), n, y.data_ptr(), ws.data_ptr(),
                                     ws.numel(), ops.stream_ptr(stream), None if tr is None else C.byref(tr)))
+        return (y, tensors) if trace else y
+
+    def forward_residual(self, h: torch.Tensor, norm: "RMSNorm", stream=None, trace: bool = False):
+        """The MoE half of a decoder layer (mlx/src/model/qwen35.rs:271-276):
+        `h + self.forward(norm.forward(h))` in one call, the normalisation fused into
+        the router's loads and the residual into the combine stage's rounding."""
+        if h.dtype != torch.bfloat16 or not h.is_cuda or h.shape[-1] != self.hidden:
+            raise IronMLXError(_lib.ERR_INVALID, "MoEMLP: h must be a bfloat16 CUDA tensor [.., hidden]")
+        h = h.contiguous()
+        n = h.numel() // self.hidden
+        y = torch.empty_like(h)
+        ws = self._ws(n, h.device)
+        cfg, w = self.config(), self.weights()
+        tr, tensors = None, None
+        if trace:
+            k, e = self.num_experts_per_tok, self.num_experts
+            i32 = dict(dtype=torch.int32, device=h.device)
+            tensors = {
+                "topk_idx": torch.empty(n, k, **i32), "topk_w": torch.empty(n, k, device=h.device),
+                "counts": torch.empty(e, **i32), "offsets": torch.empty(e + 1, **i32),
+                "perm": torch.empty(n * k, **i32), "inv_perm": torch.empty(n * k, **i32),
+                "shared_gate": torch.empty(n, device=h.device),
+            }
+            tr = MoETrace(**{name: t.data_ptr() for name, t in tensors.items()})
+        lw = None if norm.weight is None else norm.weight.data_ptr()
+        check(lib().imx_moe_forward_residual(C.byref(cfg), C.byref(w), h.data_ptr(), lw, float(norm.eps), n,
+                                             y.data_ptr(), ws.data_ptr(), ws.numel(), ops.stream_ptr(stream),
+                                             None if tr is None else C.byref(tr)))
         return (y, tensors) if trace else y
 
     def capture(self, x: torch.Tensor, x_host: Optional[torch.Tensor] = None,

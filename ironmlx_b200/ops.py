@@ -124,3 +124,19 @@ def gather_qmm(x, w, scales, biases, lhs_indices, rhs_indices, group_size=None, 
     check(lib().imx_gather_qmm(x.data_ptr(), _ptr(lhs), C.byref(qt), rhs_indices.to(torch.int32).data_ptr(),
                                n_rows, n_out, in_dim, g, b, m, y.data_ptr(), stream_ptr(stream)))
     return y
+
+
+def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, stream=None) -> torch.Tensor:
+    """`fast::rms_norm` (mlx/src/fast.rs:37-49): x * rsqrt(mean(x^2) + eps) * weight over the last
+    axis; bf16 in and out."""
+    _require_cuda(x, weight)
+    if x.dtype != torch.bfloat16 or (weight is not None and weight.dtype != torch.bfloat16):
+        raise IronMLXError(_lib.ERR_INVALID, "rms_norm: x and weight must be bfloat16")
+    h = x.shape[-1]
+    if weight is not None and weight.numel() != h:
+        raise IronMLXError(_lib.ERR_INVALID, f"rms_norm: weight has {weight.numel()} elements, rows have {h}")
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    check(lib().imx_rms_norm(x.data_ptr(), x.numel() // h, h, None if weight is None else weight.data_ptr(),
+                             float(eps), y.data_ptr(), stream_ptr(stream)))
+    return y

@@ -273,3 +273,27 @@ def rel_l2(a, b) -> float:
     b = np.asarray(b, dtype=np.float64)
     den = np.linalg.norm(b)
     return float(np.linalg.norm(a - b) / den) if den > 0 else float(np.linalg.norm(a - b))
+
+
+def rms_norm(x: np.ndarray, weight: Optional[np.ndarray], eps: float) -> np.ndarray:
+    """`fast::rms_norm` (mlx/src/fast.rs:37-49, called by RMSNorm, mlx/src/nn/norm.rs:21-24), as MLX's
+    kernels compute it for 16-bit arrays: the sum of squares and the factor in fp32, the normalised
+    value rounded to the array type, then multiplied by the weight and rounded again.
+    x: bf16-representable [N, H]; returns bf16-representable fp32."""
+    xf = np.asarray(x, np.float32)
+    inv = (1.0 / np.sqrt((xf.astype(np.float64) ** 2).mean(axis=-1, keepdims=True) + eps)).astype(np.float32)
+    t = (xf * inv).astype(F.bf16).astype(np.float32)
+    if weight is None:
+        return t
+    return (np.asarray(weight, np.float32) * t).astype(F.bf16).astype(np.float32)
+
+
+def decoder_layer_tail(h: np.ndarray, ln_weight: Optional[np.ndarray], eps: float, p: MoEParams):
+    """The MoE half of a decoder layer (mlx/src/model/qwen35.rs:271-276):
+    `normed = post_attention_layernorm(h); mlp_out = mlp(normed); h + mlp_out`, every array bf16 as the
+    reference materialises it.  Returns (y fp32 holding bf16 values, the block's trace)."""
+    normed = rms_norm(h, ln_weight, eps)
+    tr = moe_forward(normed, p)
+    mlp_out = tr.y.astype(F.bf16).astype(np.float32)
+    y = (np.asarray(h, np.float32) + mlp_out).astype(F.bf16).astype(np.float32)
+    return y, tr, normed

@@ -46,3 +46,27 @@ def moe_to_device(p: O.MoEParams, device, path="auto") -> nn.MoEMLP:
 
 def bf16_to_np(t: torch.Tensor) -> np.ndarray:
     return t.detach().float().cpu().numpy()
+
+
+def params_from_device(moe: nn.MoEMLP, top_k: int, norm: bool) -> O.MoEParams:
+    """Checker-side parameters holding the very bytes a device-built block uses."""
+    def q(ql):
+        w = ql.weight.cpu().numpy().view(np.uint32)
+        if ql.mode == "affine":
+            s = ql.scales.view(torch.int16).cpu().numpy().view(F.bf16)
+            b = ql.biases.view(torch.int16).cpu().numpy().view(F.bf16)
+        else:
+            s, b = ql.scales.cpu().numpy(), None
+        return O.QLinear(w, s, b, ql.group_size, ql.bits, ql.mode, ql.global_scale)
+
+    p = O.MoEParams(router_w=moe.gate.weight.float().cpu().numpy().astype(F.bf16),
+                    gate_up=q(moe._fused.gate_up), down=q(moe._fused.down),
+                    num_experts_per_tok=top_k, norm_topk_prob=norm)
+    if moe.shared_expert is not None:
+        p.shared_gate_proj = q(moe.shared_expert.gate_proj)
+        p.shared_up_proj = q(moe.shared_expert.up_proj)
+        p.shared_down_proj = q(moe.shared_expert.down_proj)
+        p.shared_expert_gate_w = moe.shared_expert_gate.weight.float().cpu().numpy().astype(F.bf16)
+    if moe.router_logit_bias is not None:
+        p.router_logit_bias = moe.router_logit_bias.cpu().numpy()
+    return p

@@ -11,7 +11,7 @@ from ironmlx_b200 import _lib, nn
 from ironmlx_b200.workloads import CONFIGS, MoEConfig
 from oracle import formats as F
 from oracle import moe as O
-from gpu_util import bf16_to_np, moe_to_device, t_bf16
+from gpu_util import bf16_to_np, moe_to_device, params_from_device, t_bf16
 from test_gpu_stages import FORMATS, check_routing
 from util import SMALL, TINY, make_params
 
@@ -247,3 +247,105 @@ def test_c2_reduced_experts(cuda):
     x, p, _, y, tr = run(cfg, cuda)
     err = compare(cfg, x, p, y, tr)
     print(f"c2-e32 rel-L2 {err:.3e}")
+
+
+def _full_size(cfg, cuda):
+    """A block of the benchmark's full size, built and quantized on the GPU, and the C/OpenMP
+    checker's result on the same packed bytes."""
+    from ironmlx_b200 import synthetic
+    from ironmlx_b200.workloads import Workload
+    from oracle import cref
+    moe = synthetic.build_moe(cfg, cuda)
+    x = Workload(cfg).activations()
+    p = params_from_device(moe, cfg.top_k, cfg.norm_topk_prob)
+    ref = cref.moe_forward(x, p)
+    return moe, x, p, ref
+
+
+def test_c2_full_size(cuda):
+    """The decode benchmark workload itself (256 experts, 453 MB of packed weights): against the C checker,
+    and the properties that do not depend on size — same result twice, the CUDA-graph replay equal to the
+    eager call bit for bit, and a permutation of the tokens permuting the outputs."""
+    cfg = CONFIGS["c2"]
+    moe, x, p, ref = _full_size(cfg, cuda)
+    xd = t_bf16(x, cuda)
+    y, tr = moe.forward_with_stream(xd, trace=True)
+    torch.cuda.synchronize()
+    moe.check_status()
+    yn = bf16_to_np(y)
+    clear = check_routing(tr["topk_idx"].cpu().numpy(), tr["topk_w"].cpu().numpy(), x, p, cfg.top_k, cfg.norm_topk_prob)
+    err = O.rel_l2(yn[clear], ref["y"][clear])
+    assert err <= TOL, f"c2 full size: rel-L2 {err:.3e}"
+    if clear.all():
+        assert np.array_equal(tr["perm"].cpu().numpy(), ref["perm"]) and np.array_equal(tr["counts"].cpu().numpy(), ref["counts"])
+    assert torch.equal(y, moe.forward_with_stream(xd))                        # deterministic
+    assert torch.equal(y, moe.capture(xd)().clone())                          # graph replay == eager
+    pi = np.random.default_rng(0).permutation(cfg.tokens)
+    yp, trp = moe.forward_with_stream(t_bf16(x[pi], cuda), trace=True)
+    assert torch.equal(trp["topk_idx"], tr["topk_idx"][torch.from_numpy(pi).to(cuda)])
+    assert O.rel_l2(bf16_to_np(yp), yn[pi]) < 2e-4                            # sums regroup across warps, nothing else moves
+    print(f"c2 full size rel-L2 {err:.3e}")
+
+
+def test_c3_full_size(cuda):
+    """The prefill benchmark workload (8192 tokens): tensor-memory path against the C checker and against the
+    decode kernels on the same input."""
+    cfg = CONFIGS["c3"]
+    moe, x, p, ref = _full_size(cfg, cuda)
+    xd = t_bf16(x, cuda)
+    y, tr = moe.forward_with_stream(xd, trace=True)
+    torch.cuda.synchronize()
+    moe.check_status()
+    yn = bf16_to_np(y)
+    clear = check_routing(tr["topk_idx"].cpu().numpy(), tr["topk_w"].cpu().numpy(), x, p, cfg.top_k, cfg.norm_topk_prob)
+    err = O.rel_l2(yn[clear], ref["y"][clear])
+    assert err <= TOL, f"c3 full size: rel-L2 {err:.3e}"
+    assert tr["counts"].sum().item() == cfg.tokens * cfg.top_k
+    yd = moe.forward_with_stream(xd, path="decode")
+    assert O.rel_l2(yn, bf16_to_np(yd)) < 1e-3
+    print(f"c3 full size rel-L2 {err:.3e}")
+
+
+def test_rms_norm_op(cuda):
+    from ironmlx_b200 import ops
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal((37, 512)) * 3).astype(np.float32).astype(F.bf16).astype(np.float32)
+    w = (1 + 0.2 * rng.standard_normal(512)).astype(np.float32).astype(F.bf16).astype(np.float32)
+    for weight in (w, None):
+        y = bf16_to_np(ops.rms_norm(t_bf16(x, cuda), None if weight is None else t_bf16(weight, cuda), 1e-6))
+        ref = O.rms_norm(x, weight, 1e-6)
+        # the factor's last bit can differ (summation order): at most one bf16 step on a few elements
+        assert np.mean(y != ref) < 0.02 and np.abs(y - ref).max() <= 2.0 ** -7 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("cfg", [
+    MoEConfig("tail-splitk", 48, 512, 32, 4, 512, 512, seed=61),          # router normalises its own tiles
+    MoEConfig("tail-cluster", 20, 256, 8, 2, 128, 128, seed=62),          # normalised copy + cluster router
+    MoEConfig("tail-noshared", 5, 512, 64, 6, 512, 0, seed=63),
+], ids=lambda c: c.name)
+def test_decoder_layer_tail(cuda, cfg):
+    """y = h + MoE(rms_norm(h)) in one call (qwen35.rs:271-276) against the checker's three-step version."""
+    from ironmlx_b200 import nn as inn
+    h, p = make_params(cfg)
+    h = (2.5 * h).astype(np.float32).astype(F.bf16).astype(np.float32)    # a residual stream that is not unit-variance
+    lw = (1 + 0.1 * np.random.default_rng(cfg.seed).standard_normal(cfg.hidden)).astype(np.float32).astype(F.bf16).astype(np.float32)
+    yref, tr_ref, normed_ref = O.decoder_layer_tail(h, lw, 1e-6, p)
+    moe = moe_to_device(p, cuda)
+    norm = inn.RMSNorm(t_bf16(lw, cuda), 1e-6)
+    y, tr = moe.forward_residual(t_bf16(h, cuda), norm, trace=True)
+    torch.cuda.synchronize()
+    moe.check_status()
+    yn = bf16_to_np(y)
+    # The per-row factor's last bit depends on the order of the sum of squares, which moves a few normalised
+    # values by one bf16 step: routing is checked on the GPU's own normalised rows (the fused path must make
+    # exactly the choices the unfused one makes), the output against the checker's three-step result.
+    normed = bf16_to_np(norm.forward_with_stream(t_bf16(h, cuda)))
+    assert np.mean(normed != normed_ref) < 0.02
+    clear = check_routing(tr["topk_idx"].cpu().numpy(), tr["topk_w"].cpu().numpy(), normed, p, cfg.top_k, cfg.norm_topk_prob)
+    assert O.rel_l2(yn[clear], yref[clear]) <= TOL
+    # the block's own contribution, against the unfused calls on the GPU
+    y2 = moe.forward_with_stream(norm.forward_with_stream(t_bf16(h, cuda)))
+    mlp = bf16_to_np(y2)
+    # element by element: one bf16 rounding of the sum plus the rounding the unfused block output carries
+    bound = 2.0 ** -8 * np.abs(h + mlp) + 2.0 ** -8 * np.abs(mlp) + 1e-6
+    assert np.all(np.abs(yn - (h + mlp)) <= bound)

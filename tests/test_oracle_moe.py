@@ -116,3 +116,26 @@ def test_golden_fixture(name):
 def _crc(a):
     import zlib
     return zlib.crc32(np.ascontiguousarray(a).tobytes())
+
+
+def test_rms_norm_hand_computed():
+    """x = [3, 4] (mean square 12.5), eps = 0: factor 1/sqrt(12.5); the normalised values are rounded to
+    bf16 before the weight multiplies them (fast.rs:37-49 through norm.rs:21-24)."""
+    x = np.array([[3.0, 4.0]], np.float32)
+    inv = np.float32(1.0 / np.sqrt(12.5))
+    t = (x * inv).astype(F.bf16).astype(np.float32)
+    assert np.array_equal(O.rms_norm(x, None, 0.0), t)
+    w = np.array([0.5, 3.0], np.float32)
+    assert np.array_equal(O.rms_norm(x, w, 0.0), (w * t).astype(F.bf16).astype(np.float32))
+    # eps matters for a zero row and keeps it zero
+    assert np.array_equal(O.rms_norm(np.zeros((1, 4), np.float32), np.ones(4, np.float32), 1e-6), np.zeros((1, 4)))
+
+
+def test_decoder_layer_tail_is_residual_plus_block():
+    from util import TINY, make_params
+    x, p = make_params(TINY)
+    lw = (1.0 + 0.1 * np.arange(TINY.hidden, dtype=np.float32) / TINY.hidden).astype(F.bf16).astype(np.float32)
+    y, tr, normed = O.decoder_layer_tail(x, lw, 1e-6, p)
+    again = O.moe_forward(normed, p)
+    assert np.array_equal(tr.y, again.y)
+    assert np.array_equal(y, (x + tr.y.astype(F.bf16).astype(np.float32)).astype(F.bf16).astype(np.float32))
