@@ -401,11 +401,14 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
 #pragma unroll
                 for (int T = 0; T < 2; ++T)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int slot_l = 2 * t + (i & 1);
-                        const int row = cc.pair * 32 + T * 16 + 2 * g + (i >> 1);
+                    for (int sl = 0; sl < 2; ++sl) {
+                        // rows 2g and 2g+1 of the tile are neighbours in the output row of slot 2t + sl
+                        const int slot_l = 2 * t + sl;
+                        const int row = cc.pair * 32 + T * 16 + 2 * g;
+                        const float sc = kUnscale * (sl ? c_rs1 : c_rs0);
                         if (slot_l < c_rows)
-                            a.out[(size_t)(c_slot0 + slot_l) * S.n_in + row] = acc[T][i] * (kUnscale * ((i & 1) ? c_rs1 : c_rs0));
+                            *reinterpret_cast<float2*>(a.out + (size_t)(c_slot0 + slot_l) * S.n_in + row) =
+                                make_float2(acc[T][sl] * sc, acc[T][2 + sl] * sc);
                     }
             }
         }

@@ -351,9 +351,9 @@ route_mma_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const
 // One CTA per (32 experts, K slice, 32 tokens): the two bf16 tiles are copied to
 // shared memory once, multiplied with mma.sync m16n8k16, and the fp32 partial
 // logits go to the workspace; route_finish_kernel adds the slices and does
-// softmax/top-k with one warp per token.  The CTAs of expert block 0 also
-// write their K slice of the fp16 copy of x, its group sums (for the decode
-// expert kernels) and the partial shared-gate dot product.  W_r is read once
+// softmax/top-k with one warp per token.  Every CTA also writes, for a few
+// token rows of its tile, the K slice of the fp16 copy of x, its group sums
+// (for the decode expert kernels) and the partial shared-gate dot product.  W_r is read once
 // per token block instead of once per token.
 constexpr int kSkThreads = 128;
 
@@ -422,9 +422,11 @@ route_splitk_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, co
         *reinterpret_cast<float2*>(p + (size_t)8 * E) = make_float2(acc[m][2], acc[m][3]);
     }
 
-    if (eb == 0) {
+    {
+        // fp16 copy, group sums and shared-gate partial of this K slice: the token rows of the tile are dealt
+        // out over the expert-block CTAs (row r goes to CTA r mod #blocks), then over the CTA's warps
         const int groups = H >> 6;
-        for (int r = warp * 8; r < warp * 8 + 8; ++r) {
+        for (int r = eb + warp * (int)gridDim.x; r < 32; r += 4 * (int)gridDim.x) {
             const int tok = tok0 + r;
             if (tok >= n_tokens) break;
             const __nv_bfloat16* xr = s_x + r * pad;
