@@ -79,9 +79,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y)
+// Tiled TMA copy with an L2 eviction-priority hint.
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+                 ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y), "l"(policy)
                  : "memory");
 }
 template <int OFF>
@@ -254,15 +255,19 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
             const uint32_t bar = bars + 8 * slot;
             const uint32_t wdst = wbuf + slot * kWBytes;
             mbar_expect_tx(bar, with_scales ? kWBytes + kSBytes : kWBytes);
-            tma_load_2d(wdst, &maps.w[f_map0], fc.st * 128, f_row0, bar);
-            tma_load_2d(wdst + 2048, &maps.w[f_map1], fc.st * 128, f_row1, bar);
+            // weights, scales and biases are read once per step: first in line for eviction, so that the
+            // stream does not push the activations, sums and hand-off slots out of L2 (8 % of the c2 step)
+            uint64_t policy;
+            asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+            tma_load_2d_hint(wdst, &maps.w[f_map0], fc.st * 128, f_row0, bar, policy);
+            tma_load_2d_hint(wdst + 2048, &maps.w[f_map1], fc.st * 128, f_row1, bar, policy);
             if (with_scales) {
                 const uint32_t sdst = sbuf + (n_sfetch % kStages) * kSBytes;
                 const int xs = (fc.st >> 1) * 8;
-                tma_load_2d(sdst, &maps.s[f_map0], xs, f_row0, bar);
-                tma_load_2d(sdst + 256, &maps.b[f_map0], xs, f_row0, bar);
-                tma_load_2d(sdst + 512, &maps.s[f_map1], xs, f_row1, bar);
-                tma_load_2d(sdst + 768, &maps.b[f_map1], xs, f_row1, bar);
+                tma_load_2d_hint(sdst, &maps.s[f_map0], xs, f_row0, bar, policy);
+                tma_load_2d_hint(sdst + 256, &maps.b[f_map0], xs, f_row0, bar, policy);
+                tma_load_2d_hint(sdst + 512, &maps.s[f_map1], xs, f_row1, bar, policy);
+                tma_load_2d_hint(sdst + 768, &maps.b[f_map1], xs, f_row1, bar, policy);
             }
         }
         if (with_scales) ++n_sfetch;
