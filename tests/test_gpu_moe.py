@@ -349,3 +349,23 @@ def test_decoder_layer_tail(cuda, cfg):
     # element by element: one bf16 rounding of the sum plus the rounding the unfused block output carries
     bound = 2.0 ** -8 * np.abs(h + mlp) + 2.0 ** -8 * np.abs(mlp) + 1e-6
     assert np.all(np.abs(yn - (h + mlp)) <= bound)
+
+
+@pytest.mark.parametrize("name", ["c4-nvfp4-decode", "c4-mxfp8-decode", "c5"])
+def test_other_baseline_configs_full_size(cuda, name):
+    """The remaining named workloads at their full size against the C checker: block-scaled formats at 256
+    tokens (generic kernels) and the skewed 16384-token batch (tensor-memory path, ragged experts)."""
+    cfg = CONFIGS[name]
+    moe, x, p, ref = _full_size(cfg, cuda)
+    y, tr = moe.forward_with_stream(t_bf16(x, cuda), trace=True)
+    torch.cuda.synchronize()
+    moe.check_status()
+    clear = check_routing(tr["topk_idx"].cpu().numpy(), tr["topk_w"].cpu().numpy(), x, p, cfg.top_k, cfg.norm_topk_prob,
+                          p.router_logit_bias)
+    err = O.rel_l2(bf16_to_np(y)[clear], ref["y"][clear])
+    assert err <= TOL, f"{name} full size: rel-L2 {err:.3e}"
+    counts = tr["counts"].cpu().numpy()
+    assert counts.sum() == cfg.tokens * cfg.top_k
+    if name == "c5":
+        assert counts.max() >= 0.06 * counts.sum()                         # the hottest expert holds ~8 % of the rows
+    print(f"{name} full size rel-L2 {err:.3e}, hottest expert {counts.max() / counts.sum():.3f}")
