@@ -387,12 +387,19 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     ga.act_stride = ws.act_stride;
     ga.row_scale = ws.w_of_slot;
     ga.out = ws.rows;
+    // the tensor-memory path keeps the expert rows in fp16 (in the same buffer): at its sizes the rows are the
+    // largest tensor of the step, and one extra 2^-12 rounding per row is far inside the tolerance
+    const bool rows_f16 = path == IMX_PATH_PREFILL;
+    ga.out16 = rows_f16 ? reinterpret_cast<__half*>(ws.rows) : nullptr;
     ga.status = ws.status;
     IMX_TRY(run_experts(path, ga, stream, ev ? ev[3] : nullptr));
     IMX_CHECK_CUDA(mark(4));
-    IMX_TRY(launch_combine(ws.rows, nullptr, ws.inv_perm, n_tokens, c.top_k, c.hidden,
-                           has_shared ? ws.rows + (size_t)A * c.hidden : nullptr, y, stream, false,
-                           tail != nullptr ? x : nullptr));
+    const void* shared_rows = nullptr;
+    if (has_shared)
+        shared_rows = rows_f16 ? (const void*)(reinterpret_cast<const __half*>(ws.rows) + (size_t)A * c.hidden)
+                               : (const void*)(ws.rows + (size_t)A * c.hidden);
+    IMX_TRY(launch_combine(ws.rows, nullptr, ws.inv_perm, n_tokens, c.top_k, c.hidden, shared_rows, y, stream, false,
+                           tail != nullptr ? x : nullptr, rows_f16));
     IMX_CHECK_CUDA(mark(5));
     if (trace != nullptr) {
         auto cp = [&](void* dst, const void* src, size_t bytes) -> cudaError_t {

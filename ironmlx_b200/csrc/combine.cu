@@ -16,11 +16,30 @@ constexpr int kCThreads = 128;
 constexpr int kCCols = kCThreads * 4;      // columns per CTA
 constexpr int kMaxK = 64;
 
-template <bool F32_OUT>
+// V consecutive values of a row of expert output: 4 of an fp32 row or 8 of an fp16 row (16 bytes either way)
+template <bool F16>
+__device__ __forceinline__ void load_row(const void* rows, size_t idx, float* v) {
+    if (F16) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(rows) + idx));
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+            v[2 * e] = f.x;
+            v[2 * e + 1] = f.y;
+        }
+    } else {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(rows) + idx));
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    }
+}
+
+template <bool F32_OUT, bool F16_ROWS>
 __global__ void __launch_bounds__(kCThreads)
-combine_kernel(const float* __restrict__ rows, const float* __restrict__ row_scale,
-               const int32_t* __restrict__ inv_perm, int k, int H, const float* __restrict__ shared_rows,
+combine_kernel(const void* __restrict__ rows, const float* __restrict__ row_scale,
+               const int32_t* __restrict__ inv_perm, int k, int H, const void* __restrict__ shared_rows,
                void* __restrict__ y_out, const __nv_bfloat16* __restrict__ residual) {
+    constexpr int V = F16_ROWS ? 8 : 4;          // columns per thread
     __shared__ int s_raw[kMaxK];
     __shared__ int s_slot[kMaxK];
     const int t = blockIdx.x;
@@ -38,52 +57,68 @@ combine_kernel(const float* __restrict__ rows, const float* __restrict__ row_sca
         s_slot[rank] = v;
     }
     __syncthreads();
-    const int c = blockIdx.y * kCCols + tid * 4;
+    const int c = (blockIdx.y * kCThreads + tid) * V;
     if (c >= H) return;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = 0; s0 < k; s0 += 8) {          // eight independent row loads in flight, added in order
-        float4 v[8];
-        float w[8];
+    float acc[V];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+    for (int i = 0; i < V; ++i) acc[i] = 0.f;
+    constexpr int kBatch = F16_ROWS ? 4 : 8;     // independent row loads in flight, added in order
+    for (int s0 = 0; s0 < k; s0 += kBatch) {
+        float v[kBatch][V];
+        float w[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
             const int slot = (s0 + j < k) ? s_slot[s0 + j] : -1;
-            v[j] = slot >= 0 ? __ldg(reinterpret_cast<const float4*>(rows + (size_t)slot * H + c))
-                             : make_float4(0.f, 0.f, 0.f, 0.f);      // dropped assignment (moe.rs:100)
+            if (slot >= 0) {
+                load_row<F16_ROWS>(rows, (size_t)slot * H + c, v[j]);
+            } else {                                  // dropped assignment (moe.rs:100) or past the last slot
+#pragma unroll
+                for (int i = 0; i < V; ++i) v[j][i] = 0.f;
+            }
             w[j] = (slot >= 0 && row_scale != nullptr) ? __ldg(row_scale + slot) : 1.f;
         }
         if (row_scale != nullptr) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {      // rows arrive unweighted: scale (one rounding), then add
-                acc.x += v[j].x * w[j]; acc.y += v[j].y * w[j]; acc.z += v[j].z * w[j]; acc.w += v[j].w * w[j];
-            }
+            for (int j = 0; j < kBatch; ++j)          // rows arrive unweighted: scale (one rounding), then add
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] += v[j][i] * w[j];
         } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w;
-            }
+            for (int j = 0; j < kBatch; ++j)
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] += v[j][i];
         }
     }
     if (shared_rows != nullptr) {
-        const float4 v = __ldg(reinterpret_cast<const float4*>(shared_rows + (size_t)t * H + c));
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        float v[V];
+        load_row<F16_ROWS>(shared_rows, (size_t)t * H + c, v);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] += v[i];
     }
     if (residual != nullptr) {       // the layer's residual stream (qwen35.rs:276), added before the one rounding
-        const uint2 rv = __ldg(reinterpret_cast<const uint2*>(residual + (size_t)t * H + c));
-        const float2 r0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rv.x));
-        const float2 r1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rv.y));
-        acc.x += r0.x; acc.y += r0.y; acc.z += r1.x; acc.w += r1.y;
+#pragma unroll
+        for (int i = 0; i < V; i += 2) {
+            const float2 r = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(residual + (size_t)t * H + c + i));
+            acc[i] += r.x;
+            acc[i + 1] += r.y;
+        }
     }
     if (F32_OUT) {           // partial sums of expert parallelism: summed across ranks before the rounding
-        *reinterpret_cast<float4*>(reinterpret_cast<float*>(y_out) + (size_t)t * H + c) = acc;
+        float* yf = reinterpret_cast<float*>(y_out) + (size_t)t * H + c;
+#pragma unroll
+        for (int i = 0; i < V; i += 4) *reinterpret_cast<float4*>(yf + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
         return;
     }
-    __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(y_out);
-    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
-    __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
-    uint2 o;
-    o.x = *reinterpret_cast<uint32_t*>(&lo);
-    o.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(y + (size_t)t * H + c) = o;
+    __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(y_out) + (size_t)t * H + c;
+#pragma unroll
+    for (int i = 0; i < V; i += 4) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc[i], acc[i + 1]);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(acc[i + 2], acc[i + 3]);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(y + i) = o;
+    }
 }
 
 // dst[j, :] = src[index[j], :] for rows of `row_bytes` bytes (a multiple of 4)
@@ -115,15 +150,18 @@ int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t
     return IMX_OK;
 }
 
-int launch_combine(const float* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,
-                   const float* shared_rows, void* y, cudaStream_t stream, bool f32_out, const void* residual) {
+int launch_combine(const void* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,
+                   const void* shared_rows, void* y, cudaStream_t stream, bool f32_out, const void* residual,
+                   bool rows_f16) {
     IMX_REQUIRE(k >= 1 && k <= kMaxK, "combine: top_k (%d) must be in 1..%d", k, kMaxK);
-    IMX_REQUIRE(H % 4 == 0, "combine: hidden (%d) must be a multiple of 4", H);
+    IMX_REQUIRE(H % 4 == 0 && (!rows_f16 || H % 8 == 0), "combine: hidden (%d) must be a multiple of 4 (8 for fp16 rows)", H);
     if (n == 0) return IMX_OK;
-    dim3 grid(n, ceil_div(H, kCCols));
+    dim3 grid(n, ceil_div(H, kCCols * (rows_f16 ? 2 : 1)));
     const __nv_bfloat16* res = (const __nv_bfloat16*)residual;
-    if (f32_out) combine_kernel<true><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res);
-    else combine_kernel<false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res);
+    IMX_REQUIRE(!(rows_f16 && f32_out), "combine: fp16 rows with fp32 output is not a supported combination");
+    if (rows_f16) combine_kernel<false, true><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res);
+    else if (f32_out) combine_kernel<true, false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res);
+    else combine_kernel<false, false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res);
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }

@@ -115,6 +115,7 @@ struct GroupedArgs {
     int act_stride;
     const float* row_scale;        // per slot or nullptr
     float* out;                    // fp32 [n_slots, n_in]
+    __half* out16;                 // prefill path only: the same rows as fp16 instead (out is then unused), or nullptr
     int32_t* status;               // device status word
 };
 
@@ -138,9 +139,10 @@ int make_tensor_map_2d(const void* base, CUtensorMapDataType dt, size_t esize, s
 int launch_generic_grouped(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 
 // `residual` (bf16 [n, H] or nullptr) is added to the fp32 sums before the one rounding.
-int launch_combine(const float* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,
-                   const float* shared_rows, void* y, cudaStream_t stream, bool f32_out = false,
-                   const void* residual = nullptr);
+// rows / shared_rows are fp32, or fp16 with rows_f16 (the prefill path's expert rows).
+int launch_combine(const void* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,
+                   const void* shared_rows, void* y, cudaStream_t stream, bool f32_out = false,
+                   const void* residual = nullptr, bool rows_f16 = false);
 // y = w * T(x * rsqrt(mean(x^2) + eps)) per row (y may be null), inv_out[row] = the factor (may be null).
 int launch_rms_norm(const void* x, int n, int H, const void* w, float eps, void* y, float* inv_out, cudaStream_t stream);
 int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,

@@ -385,7 +385,19 @@ prefill_umma_kernel(const GroupedArgs a, const int nt_r, const int nt_x, const i
                         __syncwarp();
                         if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[buf]));
                     }
-                    if (valid) {
+                    if (valid && a.out16 != nullptr) {
+                        // fp16 rows: half the bytes for this store and for the combine stage's reads
+                        __half* dst = a.out16 + (size_t)slot * a.set.n_in + t.ntile * 128 + h * 32;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            __half2 o[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                o[e] = __halves2half2(f32_to_f16_sat(__uint_as_float(d[i + 2 * e]) * sc),
+                                                      f32_to_f16_sat(__uint_as_float(d[i + 2 * e + 1]) * sc));
+                            *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(o);
+                        }
+                    } else if (valid) {
                         float* dst = a.out + (size_t)slot * a.set.n_in + t.ntile * 128 + h * 32;
 #pragma unroll
                         for (int i = 0; i < 32; i += 4)
