@@ -357,7 +357,7 @@ def main():
                 "layer": {"algorithmic_flops": total_flops, "achieved_tflops": total_flops / (ms * 1e-3) / 1e12,
                           "frac": total_flops / (ms * 1e-3) / 1e12 / tf_peak},
             }
-        line["gpu_launches"] = (8 if prefill else 7) * args.steps      # decode: router x2, sort, group sums, 2 products, combine
+        line["gpu_launches"] = (8 if prefill else 6) * args.steps      # decode: router x2, sort, 2 products, combine
         if rank == 0 and not args.no_cpu_baseline:
             p = host_params_from_device(moe, cfg)
             xs = wl.activations()

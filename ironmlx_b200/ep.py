@@ -360,7 +360,9 @@ class BenchRunner:
     """What bench.py drives at N > 1: `cfg.tokens` tokens per rank (weak scaling),
     experts split across the ranks."""
 
-    launches_per_step = 12
+    # kernels of this library per gathered step: router 2, sort 1, routed and shared experts 5 each (unit list,
+    # row permutation, group sums, two products), row gather 1, partial combine 1, final combine 1
+    launches_per_step = 16
 
     def __init__(self, cfg, device, rank, world):
         from .workloads import Workload
