@@ -47,8 +47,9 @@ constexpr int kSBytes = 4 * 16 * 16;           // scales, biases of tile 0, then
 // shared memory of a CTA of `warps` warps with `stages` stages each: codes | scales+biases | barriers (+ slack to
 // align the base to 1024 bytes)
 constexpr int kMaxSumGroups = 64;              // second product: groups of 64 per SwiGLU row (intermediate <= 4096)
-constexpr size_t smem_bytes(int warps, int stages, bool with_sums) {
-    return (size_t)warps * stages * (kWBytes + kSBytes + 8) + (with_sums ? (size_t)warps * 8 * kMaxSumGroups * 4 : 0) + 1024;
+// `sum_groups`: row length of the per-warp table of group sums (0: no table, first product)
+constexpr size_t smem_bytes(int warps, int stages, int sum_groups) {
+    return (size_t)warps * stages * (kWBytes + kSBytes + 8) + (size_t)warps * 8 * sum_groups * 4 + 1024;
 }
 constexpr int kSpinLimit = 1 << 20;
 constexpr int kFlagSpinLimit = 1 << 22;
@@ -167,8 +168,8 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
     const uint32_t wbuf = sbase + (uint32_t)warp * (kStages * kWBytes);
     const uint32_t sbuf = sbase + kSmemW + (uint32_t)warp * (kStages * kSBytes);
     const uint32_t bars = sbase + kSmemW + kSmemS + (uint32_t)warp * (kStages * 8);
-    // second product only: group sums of the unit's SwiGLU rows, [8 slots][kMaxSumGroups]
-    const uint32_t sums = sbase + kSmemW + kSmemS + kWarps * kStages * 8 + (uint32_t)warp * (8 * kMaxSumGroups * 4);
+    // second product only: group sums of the unit's SwiGLU rows, [8 slots][sum_groups]
+    const uint32_t sums = sbase + kSmemW + kSmemS + kWarps * kStages * 8 + (uint32_t)warp * (uint32_t)(8 * sum_groups * 4);
 
     const int n_r = a.n_units[1];
     const int stages_r = n_r * ppu_r * st_r;
@@ -329,12 +330,12 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
                         }
                     }
                     const float v = (lo + 16.f * hi) * 5.9604644775390625e-8f;
-                    asm volatile("st.shared.f32 [%0], %1;" ::"r"(sums + (uint32_t)(g * kMaxSumGroups + grp) * 4u), "f"(v) : "memory");
+                    asm volatile("st.shared.f32 [%0], %1;" ::"r"(sums + (uint32_t)(g * sum_groups + grp) * 4u), "f"(v) : "memory");
                 }
             }
             __syncwarp();
-            c_sums_a = sums + (uint32_t)((sa - u.slot0) * kMaxSumGroups) * 4u;
-            c_sums_b = sums + (uint32_t)((sb - u.slot0) * kMaxSumGroups) * 4u;
+            c_sums_a = sums + (uint32_t)((sa - u.slot0) * sum_groups) * 4u;
+            c_sums_b = sums + (uint32_t)((sb - u.slot0) * sum_groups) * 4u;
         }
     };
     setup_unit();
@@ -562,13 +563,11 @@ template <int kWarps, int kStages>
 int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn, int sms, cudaStream_t stream,
                 cudaEvent_t mid) {
     const ExpertSet& s = a.set;
-    constexpr size_t smem_gu = smem_bytes(kWarps, kStages, false), smem_dn = smem_bytes(kWarps, kStages, true);
     static bool configured = false;
     if (!configured) {
-        IMX_CHECK_CUDA(cudaFuncSetAttribute(decode_tmap_kernel<true, kWarps, kStages>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_gu));
-        IMX_CHECK_CUDA(cudaFuncSetAttribute(decode_tmap_kernel<false, kWarps, kStages>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dn));
+        constexpr int most = (int)smem_bytes(kWarps, kStages, kMaxSumGroups);
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(decode_tmap_kernel<true, kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
+        IMX_CHECK_CUDA(cudaFuncSetAttribute(decode_tmap_kernel<false, kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
         configured = true;
     }
     int grid = sms;
@@ -577,6 +576,9 @@ int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn
     const int mid_max = s.n_mid > x_mid ? s.n_mid : x_mid;
     // first product: group sums of the input rows (unless the router wrote them), then gate/up + SwiGLU
     const int g_in = s.n_in / 64, g_mid = mid_max / 64;
+    // shared memory: the rings, plus (second product) a table of group sums as wide as the rows need, so that
+    // what is not used stays with the L1 cache
+    const size_t smem_gu = smem_bytes(kWarps, kStages, 0), smem_dn = smem_bytes(kWarps, kStages, g_mid);
     if (!a.gsum_x_ready) {
         const int n = a.n_in_rows * g_in;
         group_sums_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a.in, nullptr, a.n_in_rows, g_in, s.n_in, a.gsum_x,
