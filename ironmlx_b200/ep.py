@@ -223,6 +223,14 @@ class ExpertParallelMoE:
             self._off_cache[n] = t
         return t
 
+    def _identity(self, n, dev):
+        """arange(n) on the device, made once per n."""
+        t = self._off_cache.get(("ident", n))
+        if t is None:
+            t = torch.arange(n, dtype=torch.int32, device=dev)
+            self._off_cache[("ident", n)] = t
+        return t
+
     def _all_gather(self, x):
         out = torch.empty((self.world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         if dist.get_backend(self.group) == "gloo":
@@ -270,8 +278,7 @@ class ExpertParallelMoE:
         mine = self._reduce_scatter(partial, n)
         if self.side_stream is not None and shared_rows is not None:
             torch.cuda.current_stream().wait_stream(self.side_stream)
-        ident = torch.arange(n, dtype=torch.int32, device=dev)
-        y = st.combine(mine, ident, n, 1, self.H, shared_rows)
+        y = st.combine(mine, self._identity(n, dev), n, 1, self.H, shared_rows)
         own_idx = idx[self.rank * n:(self.rank + 1) * n]
         self.last = {"topk_idx": own_idx, "topk_w": tw[self.rank * n:(self.rank + 1) * n], "counts": counts,
                      "n_recv": -1, "mode": "gathered",
