@@ -5,7 +5,7 @@
 //
 //   mirror_main <dir>
 // <dir>/meta.txt holds: tokens hidden experts top_k intermediate shared norm bits group
-// <dir>/<name>.bin are raw tensors; outputs go to <dir>/y.bin and <dir>/yq.bin.
+// <dir>/<name>.bin are raw tensors; outputs go to <dir>/y.bin, <dir>/yq.bin and <dir>/yt.bin.
 #include <cstdio>
 #include <cstdlib>
 #include <fstream>
@@ -106,6 +106,16 @@ int main(int argc, char** argv) {
         std::vector<char> hq((size_t)n * H * 2);
         check_cuda(cudaMemcpy(hq.data(), yq.ptr, hq.size(), cudaMemcpyDeviceToHost));
         std::ofstream(dir + "/yq.bin", std::ios::binary).write(hq.data(), (std::streamsize)hq.size());
+
+        // decoder-layer tail: y = h + MoE(rms_norm(h)) with the norm weight from <dir>/ln_w.bin
+        RMSNorm post_ln(Array(dev.upload(dir + "/ln_w.bin", (size_t)H * 2), {H}, Dtype::Bfloat16), 1e-6f);
+        Array yt(dev.alloc((size_t)n * H * 2), {1, n, H}, Dtype::Bfloat16);
+        moe.forward_residual(x, post_ln, yt, stream);
+        check_cuda(cudaStreamSynchronize(stream));
+        moe.check_status(stream);
+        std::vector<char> ht((size_t)n * H * 2);
+        check_cuda(cudaMemcpy(ht.data(), yt.ptr, ht.size(), cudaMemcpyDeviceToHost));
+        std::ofstream(dir + "/yt.bin", std::ios::binary).write(ht.data(), (std::streamsize)ht.size());
 
         // error convention: a wrong shape must surface as ironmlx::Error with the library's message
         bool threw = false;

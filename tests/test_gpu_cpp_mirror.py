@@ -58,6 +58,8 @@ def test_cpp_mirror_matches_ctypes_path(cuda, tmp_path):
         dump(os.path.join(d, f"{name}_w.bin"), q.w)
         dump(os.path.join(d, f"{name}_s.bin"), bf(q.scales))
         dump(os.path.join(d, f"{name}_b.bin"), bf(q.biases))
+    lw = bf(1 + 0.1 * np.random.default_rng(4).standard_normal(cfg.hidden))
+    dump(os.path.join(d, "ln_w.bin"), lw)
     rng = np.random.default_rng(3)
     xq = bf(rng.standard_normal((cfg.tokens, cfg.intermediate)).astype(np.float32))
     dump(os.path.join(d, "xq.bin"), xq)
@@ -75,3 +77,8 @@ def test_cpp_mirror_matches_ctypes_path(cuda, tmp_path):
                               t_bf16(q.biases[0], cuda), True, cfg.group_size, cfg.bits, "affine")
     yq_cpp = np.fromfile(os.path.join(d, "yq.bin"), dtype=F.bf16).astype(np.float32).reshape(cfg.tokens, cfg.hidden)
     assert np.array_equal(bf16_to_np(yq), yq_cpp)
+
+    from ironmlx_b200 import nn as inn
+    yt = bf16_to_np(moe.forward_residual(t_bf16(x, cuda), inn.RMSNorm(t_bf16(lw, cuda), 1e-6)))
+    yt_cpp = np.fromfile(os.path.join(d, "yt.bin"), dtype=F.bf16).astype(np.float32).reshape(yt.shape)
+    assert np.array_equal(yt, yt_cpp)
