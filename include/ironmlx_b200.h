@@ -15,7 +15,11 @@
  *   - work is enqueued on the given cudaStream_t (passed as void*) and the
  *     call returns without synchronising, except where stated;
  *   - no call allocates device memory: scratch comes from the caller as a
- *     workspace whose size imx_moe_workspace_bytes() reports;
+ *     workspace whose size imx_moe_workspace_bytes() reports; a workspace (and
+ *     the scratch of imx_moe_experts) is zero-filled once by the caller before
+ *     its first use: its first word is the device status word, which kernels
+ *     only ever set (a bounded wait that ran out) and imx_moe_status() reads
+ *     and clears;
  *   - one caller thread per workspace (the reference runs one engine thread
  *     per model, ironmlx/src/engine_pool.rs:79-81).
  *
@@ -58,8 +62,7 @@ extern "C" {
 #define IMX_PATH_DECODE 1       /* grouped dequant small-N tensor-core kernel */
 #define IMX_PATH_PREFILL 2      /* grouped tcgen05/TMEM GEMM fed by TMA       */
 #define IMX_PATH_GENERIC 3      /* scalar dequant-GEMV, any format            */
-#define IMX_PATH_DECODE_REGS 4  /* decode kernel, register-pipelined variant  */
-#define IMX_PATH_DECODE_BULK 5  /* decode kernel fed by per-row bulk copies   */
+/* (values above 3 select cross-check kernels: ironmlx_b200_testing.h)        */
 
 /* One quantized tensor: the (weight, scales, biases) triple of a
  * `QuantizedLinear` (mlx/src/nn/linear.rs:13-20).  biases is NULL for
@@ -162,8 +165,10 @@ IMX_API int imx_moe_forward_host(const imx_moe_config* cfg, const imx_moe_weight
                          const void* x_host, int n_tokens, void* y_host, void* workspace,
                          size_t workspace_bytes, void* stream);
 
-/* Reads (and clears) the device status word of a workspace after
- * synchronising the stream; IMX_ERR_DEVICE if a kernel recorded an error. */
+/* Reads (and clears) the device status word of a workspace -- of
+ * imx_moe_forward, or the scratch of imx_moe_experts -- after synchronising
+ * the stream; IMX_ERR_DEVICE if a kernel recorded an error (a bounded wait
+ * ran out: the call's output is incomplete). */
 IMX_API int imx_moe_status(void* workspace, void* stream);
 
 /* ── stages, for expert parallelism and stage-level parity ─────────────── */

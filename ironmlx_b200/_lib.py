@@ -8,11 +8,15 @@ from __future__ import annotations
 import ctypes as C
 import os
 
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libironmlx_b200.so")
+# IRONMLX_B200_LIB selects another build of the same library (e.g. one with different compile-time options)
+LIB_PATH = os.environ.get("IRONMLX_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)),
+                                                             "libironmlx_b200.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE = 0, 1, 2, 3, 4
 MODE = {"affine": 0, "mxfp8": 1, "nvfp4": 2}
-PATH = {"auto": 0, "decode": 1, "prefill": 2, "generic": 3, "decode_regs": 4, "decode_bulk": 5}
+PATH = {"auto": 0, "decode": 1, "prefill": 2, "generic": 3,
+        # cross-check kernels (include/ironmlx_b200_testing.h)
+        "decode_regs": 4, "prefill_plain": 5, "prefill_smem": 6}
 MODE_DEFAULTS = {"affine": (64, 4), "mxfp8": (32, 8), "nvfp4": (16, 4)}
 
 

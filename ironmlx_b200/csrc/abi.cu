@@ -4,6 +4,7 @@
 #include <cstring>
 
 #include "internal.h"
+#include "../../include/ironmlx_b200_testing.h"
 
 namespace imx {
 
@@ -125,7 +126,7 @@ int check_config(const imx_moe_config* c, QFormat* f) {
                     c->shared_intermediate % 8 == 0,
                 "shared_intermediate (%d) must be a multiple of the group size and of 8", c->shared_intermediate);
     IMX_REQUIRE(c->hidden % f->group == 0, "hidden (%d) must be a multiple of the group size (%d)", c->hidden, f->group);
-    IMX_REQUIRE(c->path >= IMX_PATH_AUTO && c->path <= IMX_PATH_DECODE_BULK, "unknown path %d", c->path);
+    IMX_REQUIRE(c->path >= IMX_PATH_AUTO && c->path <= IMX_PATH_PREFILL_SMEM, "unknown path %d", c->path);
     return IMX_OK;
 }
 
@@ -185,30 +186,45 @@ int make_expert_set(const imx_moe_config& c, const QFormat& f, const imx_qtensor
     return IMX_OK;
 }
 
+bool is_prefill(int path) {
+    return path == IMX_PATH_PREFILL || path == IMX_PATH_PREFILL_SMEM || path == IMX_PATH_PREFILL_PLAIN;
+}
+int unit_rows_for(int path) { return is_prefill(path) ? kPrefillUnitRows : kUnitRows; }
+bool is_decode(int path) { return path == IMX_PATH_DECODE || path == IMX_PATH_DECODE_REGS; }
+bool decode_supported(const ExpertSet& s) { return decode_mma_supported(s) || decode_fp_supported(s); }
+
 // Which expert kernels run for this call.  AUTO: tensor-memory GEMM tiles once
 // experts see enough rows to fill them, the decode kernels below that.
 int pick_path(const imx_moe_config& c, const ExpertSet& s, long n_rows, int* path) {
     int p = c.path;
     const bool many = n_rows >= 32L * s.num_experts;
     if (p == IMX_PATH_AUTO) {
-        if (many && prefill_umma_supported(s)) p = IMX_PATH_PREFILL;
-        else p = decode_mma_supported(s) ? IMX_PATH_DECODE : IMX_PATH_GENERIC;
+        if (many && prefill_tc_supported(s)) p = IMX_PATH_PREFILL;
+        else p = decode_supported(s) ? IMX_PATH_DECODE : IMX_PATH_GENERIC;
     }
-    IMX_REQUIRE(p != IMX_PATH_PREFILL || prefill_umma_supported(s),
-                "the prefill path supports affine 4-bit, group 64/128, sizes that are multiples of 128");
-    IMX_REQUIRE((p != IMX_PATH_DECODE && p != IMX_PATH_DECODE_REGS && p != IMX_PATH_DECODE_BULK) || decode_mma_supported(s),
-                "the decode path supports affine 2/4/8-bit, group 64/128, sizes that are multiples of 128");
+    IMX_REQUIRE(!(p == IMX_PATH_PREFILL || p == IMX_PATH_PREFILL_SMEM || p == IMX_PATH_PREFILL_PLAIN) || prefill_tc_supported(s),
+                "the prefill path supports affine 2/4/8-bit, mxfp8 and nvfp4 with hidden %% 128 == 0, intermediate %% 64 == 0 "
+                "and whole 16-byte rows of scales");
+    IMX_REQUIRE(!is_decode(p) || decode_supported(s),
+                "the decode path supports affine 2/4/8-bit (group 64/128), mxfp8 and nvfp4, sizes that are multiples of 128");
+    IMX_REQUIRE(p != IMX_PATH_DECODE_REGS || decode_mma_supported(s), "the register-pipelined decode kernel is affine only");
     *path = p;
     return IMX_OK;
 }
 
+// Order of the 16 values inside each block of the fp16 activation rows the chosen kernels read.
+void path_block_order(int path, const QFormat& f, int order[16]) {
+    if (path == IMX_PATH_GENERIC) decode_block_order(0, order);
+    else expert_block_order(f, order);
+}
+
 int run_experts(int path, const GroupedArgs& ga, cudaStream_t stream, cudaEvent_t mid = nullptr) {
-    if (path == IMX_PATH_PREFILL) return launch_prefill_umma(ga, stream, mid);
+    if (path == IMX_PATH_PREFILL) return launch_prefill_tc(ga, stream, mid, 0);
+    if (path == IMX_PATH_PREFILL_PLAIN) return launch_prefill_tc(ga, stream, mid, 1);
+    if (path == IMX_PATH_PREFILL_SMEM) return launch_prefill_tc(ga, stream, mid, 2);
+    if (is_decode(path) && decode_fp_supported(ga.set)) return launch_decode_fp(ga, stream, mid);
     if (path == IMX_PATH_DECODE && decode_tmap_supported(ga.set)) return launch_decode_tmap(ga, stream, mid);
-    if ((path == IMX_PATH_DECODE || path == IMX_PATH_DECODE_BULK) && decode_tma_supported(ga.set))
-        return launch_decode_tma(ga, stream, mid);
-    if (path == IMX_PATH_DECODE || path == IMX_PATH_DECODE_REGS || path == IMX_PATH_DECODE_BULK)
-        return launch_decode_mma(ga, stream, mid);
+    if (is_decode(path)) return launch_decode_mma(ga, stream, mid);
     return launch_generic_grouped(ga, stream, mid);
 }
 
@@ -216,12 +232,14 @@ int run_experts(int path, const GroupedArgs& ga, cudaStream_t stream, cudaEvent_
 
 namespace {
 struct ExpertsWs {
+    int32_t* status;     // [16]: [0] device status word (first in the scratch: imx_moe_status reads it there)
     int32_t* sched;
     int32_t* n_units;
     float* partials;
     WorkUnit* units;
     __half* act;
     __half* xperm;       // activations re-ordered for the decode kernels
+    __half* xs;          // activations gathered into slot order (prefill path)
     float* gsum;
     float* gsum_x;
     int max_units;
@@ -230,6 +248,7 @@ struct ExpertsWs {
 ExpertsWs carve_experts(const imx_moe_config& c, int n_rows, int n_src_rows, void* base) {
     ExpertsWs w = {};
     Carver cv(base);
+    w.status = cv.take<int32_t>(16);
     w.sched = cv.take<int32_t>(kSchedInts);
     w.n_units = cv.take<int32_t>(4);
     w.partials = cv.take<float>((size_t)kFlagWarps * 256);
@@ -237,6 +256,7 @@ ExpertsWs carve_experts(const imx_moe_config& c, int n_rows, int n_src_rows, voi
     w.units = cv.take<WorkUnit>(w.max_units);
     w.act = cv.take<__half>((size_t)n_rows * c.intermediate);
     w.xperm = cv.take<__half>((size_t)n_src_rows * c.hidden);
+    w.xs = w.xperm;      // the prefill path uses one or the other
     w.gsum = cv.take<float>((size_t)n_rows * (c.intermediate / 64 + 1));
     w.gsum_x = cv.take<float>((size_t)n_src_rows * (c.hidden / 64 + 1));
     w.bytes = align_up(cv.off, 256);
@@ -329,7 +349,7 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
 
     const int A = n_tokens * c.top_k;
     int order[16];
-    decode_block_order(path != IMX_PATH_GENERIC ? f.bits : 0, order);
+    path_block_order(path, f, order);
     auto mark = [&](int i) -> cudaError_t { return ev ? cudaEventRecord(ev[i], stream) : cudaSuccess; };
     const bool tmap_decode = path == IMX_PATH_DECODE && decode_tmap_supported(set);
     RouteScratch rscratch = {ws.route_partials, ws.route_sg, tmap_decode ? ws.gsum_x : nullptr, nullptr, nullptr};
@@ -363,7 +383,7 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     ex.n_tokens = n_tokens;
     ex.units = ws.units;
     ex.n_units = ws.n_units;
-    ex.unit_rows = path == IMX_PATH_PREFILL ? kPrefillUnitRows : kUnitRows;
+    ex.unit_rows = unit_rows_for(path);
     ex.sched = ws.sched;
     IMX_TRY(launch_sort(ws.topk_idx, A, c.num_experts, ws.counts, ws.offsets, ws.perm, ws.inv_perm,
                         ws.sort_scratch, ws.sort_scratch_bytes, &ex, stream));
@@ -385,11 +405,14 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     ga.gsum_x_ready = sums_done ? 1 : 0;
     ga.act = ws.act;
     ga.act_stride = ws.act_stride;
-    ga.row_scale = ws.w_of_slot;
+    // the tensor-core path leaves the rows unweighted: routing weight and shared-expert gate are applied by the
+    // combine stage (one multiply per row it reads anyway) instead of per element in the GEMM epilogue
+    const bool scale_in_combine = is_prefill(path);
+    ga.row_scale = scale_in_combine ? nullptr : ws.w_of_slot;
     ga.out = ws.rows;
     // the tensor-memory path keeps the expert rows in fp16 (in the same buffer): at its sizes the rows are the
     // largest tensor of the step, and one extra 2^-12 rounding per row is far inside the tolerance
-    const bool rows_f16 = path == IMX_PATH_PREFILL;
+    const bool rows_f16 = is_prefill(path);
     ga.out16 = rows_f16 ? reinterpret_cast<__half*>(ws.rows) : nullptr;
     ga.status = ws.status;
     IMX_TRY(run_experts(path, ga, stream, ev ? ev[3] : nullptr));
@@ -398,8 +421,9 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     if (has_shared)
         shared_rows = rows_f16 ? (const void*)(reinterpret_cast<const __half*>(ws.rows) + (size_t)A * c.hidden)
                                : (const void*)(ws.rows + (size_t)A * c.hidden);
-    IMX_TRY(launch_combine(ws.rows, nullptr, ws.inv_perm, n_tokens, c.top_k, c.hidden, shared_rows, y, stream, false,
-                           tail != nullptr ? x : nullptr, rows_f16));
+    IMX_TRY(launch_combine(ws.rows, scale_in_combine ? ws.w_of_slot : nullptr, ws.inv_perm, n_tokens, c.top_k, c.hidden, shared_rows,
+                           y, stream, false, tail != nullptr ? x : nullptr, rows_f16,
+                           scale_in_combine && has_shared ? ws.w_of_slot + A : nullptr));
     IMX_CHECK_CUDA(mark(5));
     if (trace != nullptr) {
         auto cp = [&](void* dst, const void* src, size_t bytes) -> cudaError_t {
@@ -576,7 +600,7 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
     IMX_TRY(make_expert_set(c, f, *gate_up, *down, num_experts, nullptr, &set));
     int path;
     IMX_TRY(pick_path(c, set, (long)n_rows, &path));
-    IMX_TRY(launch_build_units(offsets, num_experts, path == IMX_PATH_PREFILL ? kPrefillUnitRows : kUnitRows, ws.units,
+    IMX_TRY(launch_build_units(offsets, num_experts, unit_rows_for(path), ws.units,
                                ws.n_units, ws.sched, stream));
     GroupedArgs ga = {};
     ga.set = set;
@@ -585,7 +609,7 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
     if (path != IMX_PATH_GENERIC) {
         // gather the rows once, in the block order the decode kernels read
         int o[16];
-        decode_block_order(f.bits, o);
+        path_block_order(path, f, o);
         Order16 order;
         for (int i = 0; i < 16; ++i) order.o[i] = (int8_t)o[i];
         order.pair_scale_odd = path == IMX_PATH_DECODE && decode_tmap_supported(set) ? 0.0625f : 1.f;
@@ -609,8 +633,8 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
     ga.act_stride = c.intermediate;
     ga.row_scale = row_scale;
     ga.out = out;
-    ga.status = nullptr;
-    ga.xs = nullptr;
+    ga.status = ws.status;
+    ga.xs = ws.xs;
     ga.n_slots = n_rows;
     return run_experts(path, ga, stream);
 }

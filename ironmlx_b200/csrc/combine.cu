@@ -38,7 +38,8 @@ template <bool F32_OUT, bool F16_ROWS>
 __global__ void __launch_bounds__(kCThreads)
 combine_kernel(const void* __restrict__ rows, const float* __restrict__ row_scale,
                const int32_t* __restrict__ inv_perm, int k, int H, const void* __restrict__ shared_rows,
-               void* __restrict__ y_out, const __nv_bfloat16* __restrict__ residual) {
+               void* __restrict__ y_out, const __nv_bfloat16* __restrict__ residual,
+               const float* __restrict__ shared_scale) {
     constexpr int V = F16_ROWS ? 8 : 4;          // columns per thread
     __shared__ int s_raw[kMaxK];
     __shared__ int s_slot[kMaxK];
@@ -92,8 +93,9 @@ combine_kernel(const void* __restrict__ rows, const float* __restrict__ row_scal
     if (shared_rows != nullptr) {
         float v[V];
         load_row<F16_ROWS>(shared_rows, (size_t)t * H + c, v);
+        const float sw = shared_scale != nullptr ? __ldg(shared_scale + t) : 1.f;   // the shared-expert gate, when the row is ungated
 #pragma unroll
-        for (int i = 0; i < V; ++i) acc[i] += v[i];
+        for (int i = 0; i < V; ++i) acc[i] += v[i] * sw;
     }
     if (residual != nullptr) {       // the layer's residual stream (qwen35.rs:276), added before the one rounding
 #pragma unroll
@@ -152,16 +154,16 @@ int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t
 
 int launch_combine(const void* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,
                    const void* shared_rows, void* y, cudaStream_t stream, bool f32_out, const void* residual,
-                   bool rows_f16) {
+                   bool rows_f16, const float* shared_scale) {
     IMX_REQUIRE(k >= 1 && k <= kMaxK, "combine: top_k (%d) must be in 1..%d", k, kMaxK);
     IMX_REQUIRE(H % 4 == 0 && (!rows_f16 || H % 8 == 0), "combine: hidden (%d) must be a multiple of 4 (8 for fp16 rows)", H);
     if (n == 0) return IMX_OK;
     dim3 grid(n, ceil_div(H, kCCols * (rows_f16 ? 2 : 1)));
     const __nv_bfloat16* res = (const __nv_bfloat16*)residual;
     IMX_REQUIRE(!(rows_f16 && f32_out), "combine: fp16 rows with fp32 output is not a supported combination");
-    if (rows_f16) combine_kernel<false, true><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res);
-    else if (f32_out) combine_kernel<true, false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res);
-    else combine_kernel<false, false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res);
+    if (rows_f16) combine_kernel<false, true><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res, shared_scale);
+    else if (f32_out) combine_kernel<true, false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res, shared_scale);
+    else combine_kernel<false, false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res, shared_scale);
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }

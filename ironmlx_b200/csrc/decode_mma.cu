@@ -219,6 +219,10 @@ void decode_block_order(int bits, int order[16]) {
     if (bits == 2) for (int i = 0; i < 16; ++i) order[i] = Codec<2>::order(i);
 }
 
+void expert_block_order(const QFormat& f, int order[16]) {
+    decode_block_order(f.mode == IMX_MODE_AFFINE ? f.bits : 0, order);
+}
+
 bool decode_mma_supported(const ExpertSet& s) {
     const QFormat& f = s.fmt;
     if (f.mode != IMX_MODE_AFFINE) return false;

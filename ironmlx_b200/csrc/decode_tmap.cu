@@ -560,15 +560,15 @@ int make_maps(const QMat& m, size_t rows, int K, CUtensorMap* w, CUtensorMap* sc
 }
 
 template <int kWarps, int kStages>
-int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn, int sms, cudaStream_t stream,
+int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn, const DeviceInfo& di, cudaStream_t stream,
                 cudaEvent_t mid) {
     const ExpertSet& s = a.set;
-    static bool configured = false;
-    if (!configured) {
+    const int sms = di.sms;
+    if (device_needs_setup(di.ordinal, kSetupDecodeTmap)) {      // once per device, outside any stream capture
         constexpr int most = (int)smem_bytes(kWarps, kStages, kMaxSumGroups);
         IMX_CHECK_CUDA(cudaFuncSetAttribute(decode_tmap_kernel<true, kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
         IMX_CHECK_CUDA(cudaFuncSetAttribute(decode_tmap_kernel<false, kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
-        configured = true;
+        device_mark_setup(di.ordinal, kSetupDecodeTmap);
     }
     int grid = sms;
     if (grid * kWarps > kFlagWarps) grid = kFlagWarps / kWarps;
@@ -605,13 +605,8 @@ int launch_decode_tmap(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mi
                 "decode (tensor-map) path: workspace buffers missing");
     if (a.max_units == 0) return IMX_OK;
     const ExpertSet& s = a.set;
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0, v = 0;
-        IMX_CHECK_CUDA(cudaGetDevice(&dev));
-        IMX_CHECK_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
-        sms = v;
-    }
+    DeviceInfo di;
+    IMX_TRY(current_device(&di));
     DecodeMaps gu, dn;
     IMX_TRY(make_maps(s.gate, (size_t)s.num_experts * 2 * s.n_mid, s.n_in, &gu.w[0], &gu.s[0], &gu.b[0]));
     IMX_TRY(make_maps(s.down, (size_t)s.num_experts * s.n_in, s.n_mid, &dn.w[0], &dn.s[0], &dn.b[0]));
@@ -625,7 +620,7 @@ int launch_decode_tmap(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mi
     }
     dn.w[2] = dn.w[1]; dn.s[2] = dn.s[1]; dn.b[2] = dn.b[1];
     // 16 warps x 2 stages: measured best on B200 against 12 x 3, 14 x 3 and 20 x 2 (which spills at 96 registers)
-    return launch_with<16, 2>(a, gu, dn, sms, stream, mid);
+    return launch_with<16, 2>(a, gu, dn, di, stream, mid);
 }
 
 }  // namespace imx

@@ -65,6 +65,8 @@ int launch_route(const void* x, int n, int H, const void* Wr, const float* logit
 // Order of the 16 values of each block of an fp16 activation row as the
 // expert kernels of a bit width read them (identity for the generic path).
 void decode_block_order(int bits, int order[16]);
+// The same for a format: affine widths by their unpack order, mxfp8 / nvfp4 in natural order.
+void expert_block_order(const QFormat& f, int order[16]);
 
 size_t sort_scratch_bytes(int n_assign, int E);
 int launch_sort(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offsets, int32_t* perm,
@@ -125,24 +127,41 @@ int launch_decode_mma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid
 // Tensor-map fed decode kernel (affine 4-bit, group 64); the preferred decode kernel where it applies.
 bool decode_tmap_supported(const ExpertSet& s);
 int launch_decode_tmap(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
-bool decode_tma_supported(const ExpertSet& s);
-int launch_decode_tma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
-// Prefill path: tiles of kPrefillUnitRows sorted slots on tcgen05/TMEM.
-constexpr int kPrefillUnitRows = 128;
-bool prefill_umma_supported(const ExpertSet& s);
-int launch_prefill_umma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
+// Decode kernel of the block-scaled float formats (mxfp8, nvfp4).
+bool decode_fp_supported(const ExpertSet& s);
+int launch_decode_fp(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
+// Prefill path: work units of up to kPrefillUnitRows sorted slots on tcgen05/TMEM.
+constexpr int kPrefillUnitRows = 256;
+// Prefill path for every tensor-core format: the dequantized weights are the A operand, handed to the MMA
+// through tensor memory.  variant 0: as shipped; 1: one weight tile per activation tile and streamed
+// activations everywhere; 2: the dequantized tile through shared memory (1 and 2 are cross-checks).
+bool prefill_tc_supported(const ExpertSet& s);
+int launch_prefill_tc(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr, int variant = 0);
+// The current device: its ordinal and SM count (cached per device).
+struct DeviceInfo {
+    int ordinal;
+    int sms;
+};
+int current_device(DeviceInfo* out);
+// One-time set-up per (device, kernel family): attributes such as the dynamic shared-memory limit are per
+// device, so a process that drives several GPUs sets them on each.  The first call on a device should come
+// before any stream capture.
+enum { kSetupDecodeTmap = 0, kSetupPrefillTc = 1 };
+bool device_needs_setup(int ordinal, int family);
+void device_mark_setup(int ordinal, int family);
 // Tiled TMA descriptor of a 2-D row-major matrix [rows, cols] of `esize`-byte elements, `ld_bytes` between
 // rows, read in boxes of box_cols x box_rows (128-byte swizzle on request); reads past the end return zeros.
 int make_tensor_map_2d(const void* base, CUtensorMapDataType dt, size_t esize, size_t rows, size_t cols,
                        size_t ld_bytes, int box_cols, int box_rows, bool swizzle128, CUtensorMap* out,
-                       bool promote256 = false);
+                       bool promote256 = false, int swizzle_bytes = 0);   // swizzle_bytes: 32 / 64 when swizzle128 is false
 int launch_generic_grouped(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
 
 // `residual` (bf16 [n, H] or nullptr) is added to the fp32 sums before the one rounding.
 // rows / shared_rows are fp32, or fp16 with rows_f16 (the prefill path's expert rows).
 int launch_combine(const void* rows, const float* row_scale, const int32_t* inv_perm, int n, int k, int H,
                    const void* shared_rows, void* y, cudaStream_t stream, bool f32_out = false,
-                   const void* residual = nullptr, bool rows_f16 = false);
+                   const void* residual = nullptr, bool rows_f16 = false, const float* shared_scale = nullptr);
+// (shared_scale: per-token factor of the shared rows when they arrive ungated; nullptr: already gated)
 // y = w * T(x * rsqrt(mean(x^2) + eps)) per row (y may be null), inv_out[row] = the factor (may be null).
 int launch_rms_norm(const void* x, int n, int H, const void* w, float eps, void* y, float* inv_out, cudaStream_t stream);
 int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,

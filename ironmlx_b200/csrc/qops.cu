@@ -1,7 +1,7 @@
 // The reference's quantized-op surface (mlx/src/ops.rs:630-727) as standalone
 // kernels: dequantize, quantized_matmul (both transposes), plus quantize and
 // the per-row gather form.  These are the generic, any-format versions; the
-// MoE block's hot kernels live in decode_mma.cu / prefill_umma.cu.
+// MoE block's hot kernels live in decode_tmap.cu / prefill_tc.cu.
 #include <cuda_fp8.h>
 
 #include "internal.h"

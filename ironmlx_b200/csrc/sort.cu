@@ -125,6 +125,14 @@ __device__ void scan_experts(const int* s_tot, int E, int32_t* __restrict__ offs
     __syncthreads();
 }
 
+// Units of an expert with `cnt` rows.  Tensor-core tiles (unit sizes of 64 rows and more) cost the same
+// whether full or not, so an expert that needs nu of them gets nu even parts (multiples of 16 rows) instead of
+// full units and a remainder; very long lists (nu > 8, e.g. the shared expert's) keep the fixed stride.
+__device__ __forceinline__ int unit_stride(int cnt, int ur, int nu) {
+    if (ur < 64 || nu <= 1 || nu > 8) return ur;
+    return (((cnt + nu - 1) / nu) + 15) & ~15;
+}
+
 struct SortAux {
     // optional extras emitted by the fused kernel (all may be null)
     const float* topk_w;     // [A] routing weight per flat assignment
@@ -173,11 +181,12 @@ __device__ void emit_aux(const SortAux& aux, const int32_t* __restrict__ perm, c
         int nu = (cnt + ur - 1) / ur;
         int total;
         int base = block_exclusive_scan(nu, s_warp, &total);
+        const int per = unit_stride(cnt, ur, nu);
         for (int c = 0; c < nu; ++c) {
             WorkUnit u;
             u.expert = tid;
-            u.slot0 = pos0 + c * ur;
-            u.rows = min(ur, cnt - c * ur);
+            u.slot0 = pos0 + c * per;
+            u.rows = min(per, cnt - c * per);
             u.pad = 0;
             aux.units[base + c] = u;
         }
@@ -393,11 +402,12 @@ build_units_kernel(const int32_t* __restrict__ offsets, int E, int unit_rows, Wo
     const int nu = (cnt + unit_rows - 1) / unit_rows;
     int total;
     const int base = block_exclusive_scan(nu, s_warp, &total);
+    const int per = unit_stride(cnt, unit_rows, nu);
     for (int c = 0; c < nu; ++c) {
         WorkUnit u;
         u.expert = tid;
-        u.slot0 = pos0 + c * unit_rows;
-        u.rows = min(unit_rows, cnt - c * unit_rows);
+        u.slot0 = pos0 + c * per;
+        u.rows = min(per, cnt - c * per);
         u.pad = 0;
         units[base + c] = u;
     }

@@ -166,11 +166,77 @@ def test_host_io_entry_point(cuda):
     MoEConfig("pf-no-norm", 129, 512, 4, 2, 512, 512, norm_topk_prob=False, seed=37),
 ], ids=lambda c: c.name)
 def test_prefill_path_shapes(cuda, cfg):
-    """The tensor-memory GEMM path (forced) on ragged, empty and odd expert loads."""
+    """The tensor-memory GEMM path (forced) on ragged, empty and odd expert loads; the same kernel with
+    its dequantized tile in shared memory instead of tensor memory must agree with it bit for bit (same
+    operands, same MMA order)."""
     x, p, _, y, tr = run(cfg, cuda, "prefill")
     compare(cfg, x, p, y, tr)
     _, _, _, yg, _ = run(cfg, cuda, "generic", x, p)
     assert O.rel_l2(y, yg) < 1.5e-3          # fp16 weights and fp16 expert rows on one side, fp32 on the other
+    for other in ("prefill_plain", "prefill_smem"):
+        _, _, _, ys, _ = run(cfg, cuda, other, x, p)
+        assert np.array_equal(y, ys), other
+
+
+PREFILL_FORMATS = [("affine", 4, 64), ("affine", 4, 32), ("affine", 4, 128), ("affine", 8, 64), ("affine", 8, 128),
+                   ("affine", 2, 64), ("affine", 2, 32), ("mxfp8", 8, 32), ("nvfp4", 4, 16)]
+
+
+@pytest.mark.parametrize("mode,bits,group", PREFILL_FORMATS)
+def test_prefill_path_every_format(cuda, mode, bits, group):
+    """Every format of the tensor-core prefill path on ragged tiles (a wider shared expert, an expert with
+    more than 128 rows), against the checker and against the format-agnostic kernels."""
+    inter = 512 if group < 128 else 1024              # a row of scales is whole 16-byte pieces
+    cfg = MoEConfig(f"pf-{mode}{bits}g{group}", tokens=210, hidden=1024, num_experts=6, top_k=3, intermediate=inter,
+                    shared_intermediate=1024, mode=mode, bits=bits, group_size=group, seed=51)
+    x, p, _, y, tr = run(cfg, cuda, "prefill")
+    compare(cfg, x, p, y, tr)
+    _, _, _, yg, _ = run(cfg, cuda, "generic", x, p)
+    assert O.rel_l2(y, yg) < 1.5e-3
+    for other in ("prefill_plain", "prefill_smem"):   # same operands, same accumulation order
+        _, _, _, ys, _ = run(cfg, cuda, other, x, p)
+        assert np.array_equal(y, ys), other
+
+
+def test_prefill_mxfp8_wide_scale_range(cuda):
+    """mxfp8 weight rows whose block scales span many octaves (the kernel scales each block relative to its
+    row's largest exponent): rows with magnitudes from 1e-4 to 30."""
+    cfg = MoEConfig("pf-mx-range", tokens=140, hidden=512, num_experts=2, top_k=1, intermediate=512,
+                    shared_intermediate=0, mode="mxfp8", bits=8, group_size=32, seed=52)
+    from ironmlx_b200.workloads import Workload
+    from util import quantize_stack
+    wl = Workload(cfg)
+    rng = np.random.default_rng(3)
+
+    def spread(w):      # per-block magnitudes drawn log-uniformly
+        blocks = w.reshape(w.shape[0], -1, 32)
+        mag = np.exp(rng.uniform(np.log(1e-4), np.log(30.0), size=blocks.shape[:2])).astype(np.float32)
+        return (blocks * mag[..., None]).reshape(w.shape).astype(np.float32)
+
+    x = wl.activations()
+    p = O.MoEParams(router_w=wl.router_weight().astype(F.bf16),
+                    gate_up=quantize_stack([spread(wl.expert_gate_up(e)) * 0.05 for e in range(2)], cfg),
+                    down=quantize_stack([spread(wl.expert_down(e)) * 0.05 for e in range(2)], cfg),
+                    num_experts_per_tok=1, norm_topk_prob=True)
+    for path in ("prefill", "decode"):
+        x, p, _, y, tr = run(cfg, cuda, path, x, p)
+        compare(cfg, x, p, y, tr)
+
+
+@pytest.mark.parametrize("mode,bits,group", [("mxfp8", 8, 32), ("nvfp4", 4, 16)])
+@pytest.mark.parametrize("cfg", [
+    MoEConfig("fp-base", 40, 256, 8, 3, 128, 256, seed=71),
+    MoEConfig("fp-one-token", 1, 512, 8, 2, 256, 128, seed=72),
+    MoEConfig("fp-no-shared", 33, 384, 16, 4, 128, 0, seed=73),
+    MoEConfig("fp-crowded", 100, 128, 2, 2, 256, 128, seed=74),
+], ids=lambda c: c.name)
+def test_decode_path_float_formats(cuda, cfg, mode, bits, group):
+    """mxfp8 / nvfp4 on their decode kernel, against the checker and the format-agnostic kernels."""
+    cfg = cfg.with_(name=f"{cfg.name}-{mode}", mode=mode, bits=bits, group_size=group)
+    x, p, _, y, tr = run(cfg, cuda, "decode")
+    compare(cfg, x, p, y, tr)
+    _, _, _, yg, _ = run(cfg, cuda, "generic", x, p)
+    assert O.rel_l2(y, yg) < 1e-3
 
 
 def test_prefill_path_refuses_unsupported_shapes(cuda):
@@ -203,10 +269,10 @@ def test_prefill_shape_reduced(cuda, group):
 ], ids=lambda c: c.name)
 def test_decode_tensor_map_kernel(cuda, cfg):
     """Shapes the tensor-map fed decode kernel takes (4-bit, group 64, sizes % 512 == 0): against the
-    checker, and against the bulk-copy decode kernel, which shares none of its data movement."""
+    checker, and against the register-pipelined decode kernel, which shares none of its data movement."""
     x, p, _, y, tr = run(cfg, cuda, "decode")
     compare(cfg, x, p, y, tr)
-    _, _, _, yb, _ = run(cfg, cuda, "decode_bulk", x, p)
+    _, _, _, yb, _ = run(cfg, cuda, "decode_regs", x, p)
     assert O.rel_l2(y, yb) < 1e-3
 
 
@@ -351,10 +417,12 @@ def test_decoder_layer_tail(cuda, cfg):
     assert np.all(np.abs(yn - (h + mlp)) <= bound)
 
 
-@pytest.mark.parametrize("name", ["c4-nvfp4-decode", "c4-mxfp8-decode", "c5"])
+@pytest.mark.parametrize("name", ["c4-nvfp4-decode", "c4-mxfp8-decode", "c4-nvfp4-prefill", "c4-mxfp8-prefill",
+                                  "c5", "c5-2bit", "c5-8bit"])
 def test_other_baseline_configs_full_size(cuda, name):
     """The remaining named workloads at their full size against the C checker: block-scaled formats at 256
-    tokens (generic kernels) and the skewed 16384-token batch (tensor-memory path, ragged experts)."""
+    tokens (their decode kernel) and 4096 tokens (tensor-core path), and the skewed 16384-token batch at 4-, 2-
+    and 8-bit (tensor-core path, ragged experts)."""
     cfg = CONFIGS[name]
     moe, x, p, ref = _full_size(cfg, cuda)
     y, tr = moe.forward_with_stream(t_bf16(x, cuda), trace=True)
@@ -366,6 +434,6 @@ def test_other_baseline_configs_full_size(cuda, name):
     assert err <= TOL, f"{name} full size: rel-L2 {err:.3e}"
     counts = tr["counts"].cpu().numpy()
     assert counts.sum() == cfg.tokens * cfg.top_k
-    if name == "c5":
+    if name.startswith("c5"):
         assert counts.max() >= 0.06 * counts.sum()                         # the hottest expert holds ~8 % of the rows
     print(f"{name} full size rel-L2 {err:.3e}, hottest expert {counts.max() / counts.sum():.3f}")
