@@ -121,6 +121,11 @@ IMX_API const char* imx_last_error(void);
 /* Library version string. */
 IMX_API const char* imx_version(void);
 
+/* Number of kernels the library has launched in this process so far (launches
+ * recorded into a stream capture count once, when they are recorded).  For
+ * measurement: the difference around a call is the call's launch count. */
+IMX_API unsigned long long imx_launch_count(void);
+
 /* ── the block: MoEMLP::forward_with_stream, mlx/src/nn/moe.rs:55-183 ───── */
 
 /* Scratch bytes imx_moe_forward needs for up to n_tokens tokens. */
@@ -260,6 +265,48 @@ IMX_API int imx_moe_combine_partial(const float* rows, const float* row_scale, c
  * of the expert-parallel exchange. */
 IMX_API int imx_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,
                     void* stream);
+
+/* ── expert parallelism (no counterpart in the reference, which has no
+ *    distributed code: it shards the expert loop of moe.rs:117-144) ────── */
+
+/* One process per GPU.  Rank r of R owns experts [r*E/R, (r+1)*E/R): its
+ * imx_moe_weights holds gate_up / down of THOSE experts only ([E/R, 2I, .] and
+ * [E/R, H, .]); router_w covers all E experts, the shared expert and its gate
+ * are replicated.  Every rank brings the same number of tokens.  Collectives run
+ * on NCCL, which the library loads at run time (the copy already in the
+ * process, else libnccl.so.2). */
+typedef struct imx_ep_ctx imx_ep_ctx;
+
+#define IMX_EP_UNIQUE_ID_BYTES 128
+#define IMX_EP_AUTO 0        /* gathered up to 1023 tokens over all ranks, else all-to-all */
+#define IMX_EP_GATHERED 1    /* all-gather tokens, local experts, reduce-scatter fp32 partial sums: fixed shapes,
+                                no host synchronisation (can be captured in a CUDA graph) */
+#define IMX_EP_ALL_TO_ALL 2  /* dispatch / return of fp16 rows by grouped ncclSend / ncclRecv; one host
+                                synchronisation per call (the exchange's split sizes); results are bit-identical to
+                                imx_moe_forward on one GPU; needs a format/shape the tensor-core kernels take */
+
+typedef struct imx_ep_info {
+    int schedule;                        /* the schedule that ran                          */
+    long long rows_received;             /* all-to-all: rows this rank's experts processed */
+    unsigned long long bytes_sent;       /* bytes this rank put on the wire in the call    */
+    unsigned long long bytes_received;
+} imx_ep_info;
+
+/* An NCCL unique id (rank 0 makes one and hands it to the others by whatever means the host has). */
+IMX_API int imx_ep_unique_id(void* id128);
+/* Collective: builds this rank's context and its own communicator from the id.  cfg describes the whole
+ * block (num_experts = E). */
+IMX_API int imx_ep_create(const imx_moe_config* cfg, const void* unique_id, int rank, int world, imx_ep_ctx** ctx);
+/* The same on a communicator the host already has (an ncclComm_t); it is borrowed, not destroyed. */
+IMX_API int imx_ep_create_from_comm(const imx_moe_config* cfg, void* nccl_comm, int rank, int world, imx_ep_ctx** ctx);
+IMX_API int imx_ep_destroy(imx_ep_ctx* ctx);
+/* Scratch bytes for n_local tokens per rank (all-to-all: sized for every assignment of every rank landing here). */
+IMX_API int imx_ep_workspace_bytes(const imx_ep_ctx* ctx, int n_local, int schedule, size_t* bytes);
+/* y[n_local, H] = MoE(x[n_local, H]) with the experts spread over the ranks.  Collective: every rank calls it
+ * with the same n_local and schedule.  workspace: zero-filled once, 256-byte aligned; imx_moe_status() reads its
+ * status word.  info may be NULL. */
+IMX_API int imx_ep_forward(imx_ep_ctx* ctx, const imx_moe_weights* local_weights, const void* x, int n_local, void* y,
+                   void* workspace, size_t workspace_bytes, void* stream, int schedule, imx_ep_info* info);
 
 /* ── the reference's quantized-op surface, mlx/src/ops.rs:630-727 ──────── */
 

@@ -38,6 +38,14 @@ class MoEWeights(C.Structure):
                 ("shared_expert_gate_w", C.c_void_p)]
 
 
+class EpInfo(C.Structure):
+    _fields_ = [("schedule", C.c_int), ("rows_received", C.c_longlong), ("bytes_sent", C.c_ulonglong),
+                ("bytes_received", C.c_ulonglong)]
+
+
+EP_SCHEDULE = {"auto": 0, "gathered": 1, "a2a": 2}
+
+
 class MoETrace(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
         "topk_idx", "topk_w", "counts", "offsets", "perm", "inv_perm", "shared_gate")]
@@ -48,6 +56,7 @@ _vp, _i, _f, _sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
 SIGNATURES = {
     "imx_last_error": (C.c_char_p, []),
     "imx_version": (C.c_char_p, []),
+    "imx_launch_count": (C.c_ulonglong, []),
     "imx_moe_workspace_bytes": (_i, [C.POINTER(MoEConfig), _i, C.POINTER(_sz)]),
     "imx_moe_forward": (_i, [C.POINTER(MoEConfig), C.POINTER(MoEWeights), _vp, _i, _vp, _vp, _sz, _vp,
                              C.POINTER(MoETrace)]),
@@ -71,6 +80,12 @@ SIGNATURES = {
     "imx_moe_combine_scaled": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "imx_moe_combine_partial": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "imx_gather_rows": (_i, [_vp, _vp, _i, _sz, _vp, _vp]),
+    "imx_ep_unique_id": (_i, [_vp]),
+    "imx_ep_create": (_i, [C.POINTER(MoEConfig), _vp, _i, _i, C.POINTER(_vp)]),
+    "imx_ep_create_from_comm": (_i, [C.POINTER(MoEConfig), _vp, _i, _i, C.POINTER(_vp)]),
+    "imx_ep_destroy": (_i, [_vp]),
+    "imx_ep_workspace_bytes": (_i, [_vp, _i, _i, C.POINTER(_sz)]),
+    "imx_ep_forward": (_i, [_vp, C.POINTER(MoEWeights), _vp, _i, _vp, _vp, _sz, _vp, _i, C.POINTER(EpInfo)]),
     "imx_dequantize": (_i, [C.POINTER(QTensor), _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "imx_quantized_matmul": (_i, [_vp, _i, C.POINTER(QTensor), _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "imx_quantize": (_i, [_vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp]),

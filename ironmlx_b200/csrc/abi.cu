@@ -20,20 +20,7 @@ void set_error(const char* fmt, ...) {
 }
 const char* last_error() { return g_error.c_str(); }
 
-namespace {
-
-struct Carver {
-    uint8_t* base;
-    size_t off = 0;
-    explicit Carver(void* p) : base((uint8_t*)p) {}
-    template <typename T>
-    T* take(size_t count) {
-        off = align_up(off, 256);
-        T* p = base ? (T*)(base + off) : nullptr;
-        off += count * sizeof(T);
-        return p;
-    }
-};
+// (the helpers below are shared with the expert-parallel layer, ep.cu: declared in internal.h)
 
 // Workspace of the fused forward.
 struct ForwardWs {
@@ -218,7 +205,7 @@ void path_block_order(int path, const QFormat& f, int order[16]) {
     else expert_block_order(f, order);
 }
 
-int run_experts(int path, const GroupedArgs& ga, cudaStream_t stream, cudaEvent_t mid = nullptr) {
+int run_experts(int path, const GroupedArgs& ga, cudaStream_t stream, cudaEvent_t mid) {
     if (path == IMX_PATH_PREFILL) return launch_prefill_tc(ga, stream, mid, 0);
     if (path == IMX_PATH_PREFILL_PLAIN) return launch_prefill_tc(ga, stream, mid, 1);
     if (path == IMX_PATH_PREFILL_SMEM) return launch_prefill_tc(ga, stream, mid, 2);
@@ -228,7 +215,7 @@ int run_experts(int path, const GroupedArgs& ga, cudaStream_t stream, cudaEvent_
     return launch_generic_grouped(ga, stream, mid);
 }
 
-}  // namespace
+
 
 namespace {
 struct ExpertsWs {
@@ -303,7 +290,8 @@ using namespace imx;
 extern "C" {
 
 const char* imx_last_error(void) { return last_error(); }
-const char* imx_version(void) { return "ironmlx_b200 0.1 (sm_100a)"; }
+const char* imx_version(void) { return "ironmlx_b200 0.2 (sm_100a)"; }
+unsigned long long imx_launch_count(void) { return launch_count(); }
 
 int imx_moe_workspace_bytes(const imx_moe_config* cfg, int n_tokens, size_t* bytes) {
     QFormat f;
@@ -614,7 +602,7 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
         for (int i = 0; i < 16; ++i) order.o[i] = (int8_t)o[i];
         order.pair_scale_odd = path == IMX_PATH_DECODE && decode_tmap_supported(set) ? 0.0625f : 1.f;
         permute_rows_kernel<<<n_rows, 256, 0, stream>>>((const __half*)x_f16, row_index, c.hidden, ws.xperm, order,
-                                                        offsets + num_experts);
+                                                        offsets + num_experts); IMX_LAUNCHED();
         IMX_CHECK_CUDA(cudaGetLastError());
         ga.in = ws.xperm;
         ga.row_index = nullptr;

@@ -147,7 +147,7 @@ int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t
     if (n_rows == 0) return IMX_OK;
     const int words = (int)(row_bytes / 4);
     const int threads = words >= 1024 ? 256 : (words >= 128 ? 128 : 32);
-    gather_rows_kernel<<<n_rows, threads, 0, stream>>>((const uint32_t*)src, index, words, (uint32_t*)dst);
+    gather_rows_kernel<<<n_rows, threads, 0, stream>>>((const uint32_t*)src, index, words, (uint32_t*)dst); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }
@@ -163,7 +163,7 @@ int launch_combine(const void* rows, const float* row_scale, const int32_t* inv_
     IMX_REQUIRE(!(rows_f16 && f32_out), "combine: fp16 rows with fp32 output is not a supported combination");
     if (rows_f16) combine_kernel<false, true><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res, shared_scale);
     else if (f32_out) combine_kernel<true, false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res, shared_scale);
-    else combine_kernel<false, false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res, shared_scale);
+    else combine_kernel<false, false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res, shared_scale); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }

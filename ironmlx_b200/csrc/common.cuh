@@ -41,6 +41,11 @@ const char* last_error();
         if (_s != IMX_OK) return _s;    \
     } while (0)
 
+// Every kernel launch of the library is counted (a process-wide counter read through imx_launch_count):
+// callers that replay a captured graph multiply the launches recorded during capture by their replays.
+void count_launch();
+#define IMX_LAUNCHED() ::imx::count_launch()
+
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 

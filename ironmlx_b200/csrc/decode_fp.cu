@@ -366,10 +366,10 @@ int launch_mode(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid) {
     IMX_CHECK_CUDA(cudaGetDevice(&dev));
     IMX_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int mid_max = s.has_extra && s.x_mid > s.n_mid ? s.x_mid : s.n_mid;
-    decode_fp_kernel<MX, true><<<sms, kThreads, 0, stream>>>(a, mid_max / 16);
+    decode_fp_kernel<MX, true><<<sms, kThreads, 0, stream>>>(a, mid_max / 16); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
-    decode_fp_kernel<MX, false><<<sms, kThreads, 0, stream>>>(a, s.n_in / 32);
+    decode_fp_kernel<MX, false><<<sms, kThreads, 0, stream>>>(a, s.n_in / 32); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }

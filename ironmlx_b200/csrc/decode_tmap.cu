@@ -582,16 +582,16 @@ int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn
     if (!a.gsum_x_ready) {
         const int n = a.n_in_rows * g_in;
         group_sums_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a.in, nullptr, a.n_in_rows, g_in, s.n_in, a.gsum_x,
-                                                             a.n_rows_dev);
+                                                             a.n_rows_dev); IMX_LAUNCHED();
         IMX_CHECK_CUDA(cudaGetLastError());
     }
     decode_tmap_kernel<true, kWarps, kStages><<<grid, kWarps * 32, smem_gu, stream>>>(
-        a, s.n_mid / 16, x_mid / 16, s.n_in / kStageCodes, s.n_in / kStageCodes, 8, g_in, gu);
+        a, s.n_mid / 16, x_mid / 16, s.n_in / kStageCodes, s.n_in / kStageCodes, 8, g_in, gu); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
     // second product: every warp sums the groups of its unit's SwiGLU rows itself
     decode_tmap_kernel<false, kWarps, kStages><<<grid, kWarps * 32, smem_dn, stream>>>(
-        a, s.n_in / 32, s.n_in / 32, s.n_mid / kStageCodes, x_mid / kStageCodes, 8 + kFlagWarps, g_mid, dn);
+        a, s.n_in / 32, s.n_in / 32, s.n_mid / kStageCodes, x_mid / kStageCodes, 8 + kFlagWarps, g_mid, dn); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }

@@ -162,7 +162,7 @@ int launch_generic_grouped(const GroupedArgs& a, cudaStream_t stream, cudaEvent_
         IMX_REQUIRE(smem <= 200 * 1024, "experts: hidden size %d too large for the generic path", s.n_in);
         IMX_CHECK_CUDA(cudaFuncSetAttribute(generic_grouped_kernel<true>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        generic_grouped_kernel<true><<<a.max_units * rb, kGThreads, smem, stream>>>(a, rb);
+        generic_grouped_kernel<true><<<a.max_units * rb, kGThreads, smem, stream>>>(a, rb); IMX_LAUNCHED();
         IMX_CHECK_CUDA(cudaGetLastError());
         if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
     }
@@ -172,7 +172,7 @@ int launch_generic_grouped(const GroupedArgs& a, cudaStream_t stream, cudaEvent_
         IMX_REQUIRE(smem <= 200 * 1024, "experts: intermediate size %d too large for the generic path", mid_max);
         IMX_CHECK_CUDA(cudaFuncSetAttribute(generic_grouped_kernel<false>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        generic_grouped_kernel<false><<<a.max_units * rb, kGThreads, smem, stream>>>(a, rb);
+        generic_grouped_kernel<false><<<a.max_units * rb, kGThreads, smem, stream>>>(a, rb); IMX_LAUNCHED();
         IMX_CHECK_CUDA(cudaGetLastError());
     }
     return IMX_OK;

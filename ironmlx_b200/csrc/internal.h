@@ -39,7 +39,8 @@ struct SortExtras {
     int32_t* tok_of_slot = nullptr;
     float* w_of_slot = nullptr;
     const float* shared_gate = nullptr;
-    int n_tokens = 0;
+    int n_tokens = 0;                 // tokens the shared expert serves: slots [n_assign, n_assign + n_tokens)
+    int shared_token0 = 0;            // ... namely tokens shared_token0 .. shared_token0 + n_tokens - 1
     WorkUnit* units = nullptr;
     int32_t* n_units = nullptr;
     int unit_rows = kUnitRows;
@@ -118,6 +119,7 @@ struct GroupedArgs {
     const float* row_scale;        // per slot or nullptr
     float* out;                    // fp32 [n_slots, n_in]
     __half* out16;                 // prefill path only: the same rows as fp16 instead (out is then unused), or nullptr
+    const int32_t* out_index;      // prefill path only: output row of each slot (nullptr: the slot itself)
     int32_t* status;               // device status word
 };
 
@@ -143,6 +145,7 @@ struct DeviceInfo {
     int sms;
 };
 int current_device(DeviceInfo* out);
+unsigned long long launch_count();   // kernels this library has launched (or recorded into a capture) so far
 // One-time set-up per (device, kernel family): attributes such as the dynamic shared-memory limit are per
 // device, so a process that drives several GPUs sets them on each.  The first call on a device should come
 // before any stream capture.
@@ -167,9 +170,10 @@ int launch_rms_norm(const void* x, int n, int H, const void* w, float eps, void*
 int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,
                        cudaStream_t stream);
 
-// Builds the unit list for a caller-given offsets array (stage-level API).
+// Builds the unit list for a caller-given offsets array (stage-level API).  extra_from >= 0: the units of that
+// (last) expert are listed as the extra expert's.
 int launch_build_units(const int32_t* offsets, int E, int unit_rows, WorkUnit* units, int32_t* n_units,
-                       int32_t* sched, cudaStream_t stream);
+                       int32_t* sched, cudaStream_t stream, int extra_from = -1);
 
 int launch_dequantize(const QMat& w, int rows, int in, QFormat f, int out_dtype, void* out,
                       cudaStream_t stream);
@@ -180,5 +184,29 @@ int launch_qmm(const void* x, int m, const QMat& w, int n_out, int in, int trans
                cudaStream_t stream);
 
 int validate_format(int mode, int bits, int group, QFormat* out);
+
+// ── pieces of the fused forward shared with the expert-parallel layer ─────────
+// Hands out 256-byte aligned pieces of a caller-provided buffer (base == nullptr: only sizes).
+struct Carver {
+    uint8_t* base;
+    size_t off = 0;
+    explicit Carver(void* p) : base((uint8_t*)p) {}
+    template <typename T>
+    T* take(size_t count) {
+        off = align_up(off, 256);
+        T* p = base ? (T*)(base + off) : nullptr;
+        off += count * sizeof(T);
+        return p;
+    }
+};
+int check_config(const imx_moe_config* c, QFormat* f);
+int make_expert_set(const imx_moe_config& c, const QFormat& f, const imx_qtensor& gate_up, const imx_qtensor& down,
+                    int num_experts, const imx_moe_weights* shared, ExpertSet* out);
+int pick_path(const imx_moe_config& c, const ExpertSet& s, long n_rows, int* path);
+void path_block_order(int path, const QFormat& f, int order[16]);
+int run_experts(int path, const GroupedArgs& ga, cudaStream_t stream, cudaEvent_t mid = nullptr);
+bool is_prefill(int path);
+int unit_rows_for(int path);
+int max_units_for(int A, int E, int n_shared_tokens);
 
 }  // namespace imx

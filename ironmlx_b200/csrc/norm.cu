@@ -58,7 +58,7 @@ int launch_rms_norm(const void* x, int n, int H, const void* w, float eps, void*
                 "rms_norm: arrays must be 16-byte aligned");
     if (n == 0) return IMX_OK;
     rms_norm_kernel<<<ceil_div(n, 8), 256, 0, stream>>>((const __nv_bfloat16*)x, n, H, (const __nv_bfloat16*)w, eps,
-                                                        (__nv_bfloat16*)y, inv_out);
+                                                        (__nv_bfloat16*)y, inv_out); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }

@@ -761,7 +761,19 @@ prefill_tc_kernel(const GroupedArgs a, const TcParams p, const __grid_constant__
                     }
                     const size_t o0 = (size_t)(t.slot0 + c * 32) * a.set.n_in + col;
                     const int n_ok = t.rows - c * 32;
-                    if (a.out16 != nullptr) {
+                    if (a.out16 != nullptr && a.out_index != nullptr) {
+                        // rows scattered to the positions the caller names (expert parallelism: straight into the
+                        // buffer the rows travel back in): one index per lane, handed round by shuffle
+                        const int my = c * 32 + lane;
+                        const int orow = my < t.rows ? a.out_index[t.slot0 + my] : 0;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const uint32_t h = pack_f16_sat(o[i], o[i + 1]);
+                            const int r0 = __shfl_sync(0xffffffffu, orow, i), r1 = __shfl_sync(0xffffffffu, orow, i + 1);
+                            if (i < n_ok) st_global_u16(a.out16 + (size_t)r0 * a.set.n_in + col, h);
+                            if (i + 1 < n_ok) st_global_u16(a.out16 + (size_t)r1 * a.set.n_in + col, h >> 16);
+                        }
+                    } else if (a.out16 != nullptr) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
                             const uint32_t h = pack_f16_sat(o[i], o[i + 1]);
@@ -939,11 +951,13 @@ int launch_fmt(const GroupedArgs& a, const Plan& gu, const Plan& dn, bool ts, co
     if (!ts) prefill_tc_kernel<true, FMT, false, false, false><<<sms, kThreadsTc, gu.smem, stream>>>(a, gu.p, mgu);
     else if (gu.wide) prefill_tc_kernel<true, FMT, true, true, false><<<sms, kThreadsTc, gu.smem, stream>>>(a, gu.p, mgu);
     else prefill_tc_kernel<true, FMT, true, false, false><<<sms, kThreadsTc, gu.smem, stream>>>(a, gu.p, mgu);
+    IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
     if (!ts) prefill_tc_kernel<false, FMT, false, false, false><<<sms, kThreadsTc, dn.smem, stream>>>(a, dn.p, mdn);
     else if (dn.xr) prefill_tc_kernel<false, FMT, true, false, true><<<sms, kThreadsTc, dn.smem, stream>>>(a, dn.p, mdn);
     else prefill_tc_kernel<false, FMT, true, false, false><<<sms, kThreadsTc, dn.smem, stream>>>(a, dn.p, mdn);
+    IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }

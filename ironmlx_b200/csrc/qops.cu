@@ -260,6 +260,7 @@ int launch_dequantize(const QMat& w, int rows, int in, QFormat f, int out_dtype,
     else if (out_dtype == 1) dequantize_kernel<<<blocks, 256, 0, stream>>>(w, rows, in, f, (float*)out);
     else if (out_dtype == 2) dequantize_kernel<<<blocks, 256, 0, stream>>>(w, rows, in, f, (__half*)out);
     else IMX_REQUIRE(false, "dequantize: out_dtype must be 0 (bf16), 1 (fp32) or 2 (fp16)");
+    IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }
@@ -273,7 +274,7 @@ int launch_quantize(const float* w, int rows, int in, QFormat f, float gscale, v
     const long n = (long)rows * (in / f.group);
     if (n == 0) return IMX_OK;
     quantize_kernel<<<(int)((n + 127) / 128), 128, 0, stream>>>(w, rows, in, f, gscale, (uint8_t*)wp,
-                                                                (uint8_t*)scales, (uint8_t*)biases);
+                                                                (uint8_t*)scales, (uint8_t*)biases); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }
@@ -292,7 +293,7 @@ int launch_qmm(const void* x, int m, const QMat& w, int n_out, int in, int trans
         dim3 grid(ceil_div(m, rows_per_cta), ceil_div(n_out, kQOut));
         qmm_t_kernel<<<grid, kQThreads, smem, stream>>>((const __nv_bfloat16*)x, m, w, n_out, in, f,
                                                         (__nv_bfloat16*)y, lhs_index, rhs_index, w_stride,
-                                                        s_stride, rows_per_cta);
+                                                        s_stride, rows_per_cta); IMX_LAUNCHED();
     } else {
         IMX_REQUIRE(lhs_index == nullptr && rhs_index == nullptr, "gather form requires transpose");
         const size_t smem = (size_t)kQRows * n_out * sizeof(float);
@@ -300,7 +301,7 @@ int launch_qmm(const void* x, int m, const QMat& w, int n_out, int in, int trans
         IMX_CHECK_CUDA(cudaFuncSetAttribute(qmm_n_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         dim3 grid(ceil_div(m, kQRows), ceil_div(in, kQThreads * 8));
         qmm_n_kernel<<<grid, kQThreads, smem, stream>>>((const __nv_bfloat16*)x, m, w, n_out, in, f,
-                                                        (__nv_bfloat16*)y);
+                                                        (__nv_bfloat16*)y); IMX_LAUNCHED();
     }
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;

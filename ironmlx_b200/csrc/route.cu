@@ -531,7 +531,7 @@ int launch_route_mma(const void* x, int n, int H, const void* Wr, const float* l
     IMX_CHECK_CUDA(cudaFuncSetAttribute(route_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     route_mma_kernel<NT><<<ceil_div(n, kRT), kRThreads, smem, stream>>>(
         (const __nv_bfloat16*)x, n, H, (const __nv_bfloat16*)Wr, logit_bias, k, norm, (const __nv_bfloat16*)w_sg,
-        topk_idx, topk_w, shared_gate, (__half*)x16, order);
+        topk_idx, topk_w, shared_gate, (__half*)x16, order); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }
@@ -564,10 +564,10 @@ int launch_route(const void* x, int n, int H, const void* Wr, const float* logit
         const dim3 grid((unsigned)(E / 32), (unsigned)(H / ks), (unsigned)ceil_div(n, 32));
         route_splitk_kernel<<<grid, kSkThreads, tiles, stream>>>(
             (const __nv_bfloat16*)x, n, H, (const __nv_bfloat16*)Wr, logit_bias, E, k, norm, (const __nv_bfloat16*)w_sg,
-            topk_idx, topk_w, shared_gate, (__half*)x16, order, ks, *rs);
+            topk_idx, topk_w, shared_gate, (__half*)x16, order, ks, *rs); IMX_LAUNCHED();
         IMX_CHECK_CUDA(cudaGetLastError());
         route_finish_kernel<<<ceil_div(n, kSkThreads / 32), kSkThreads, (size_t)(kSkThreads / 32) * E * sizeof(float), stream>>>(
-            n, (int)grid.z * 32, (int)grid.y, logit_bias, E, k, norm, w_sg != nullptr, topk_idx, topk_w, shared_gate, *rs);
+            n, (int)grid.z * 32, (int)grid.y, logit_bias, E, k, norm, w_sg != nullptr, topk_idx, topk_w, shared_gate, *rs); IMX_LAUNCHED();
         IMX_CHECK_CUDA(cudaGetLastError());
         if (sums_done != nullptr) *sums_done = rs->gsum_x != nullptr;
         return IMX_OK;

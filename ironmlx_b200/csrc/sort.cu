@@ -141,6 +141,7 @@ struct SortAux {
     float* w_of_slot;        // [A (+N)] routing weight per sorted slot
     const float* shared_gate;// [N] or null: appended after the A routed slots
     int n_tokens;
+    int shared_token0;       // first of the n_tokens tokens the shared expert serves (0 unless tokens are sharded)
     WorkUnit* units;         // work units of `unit_rows` rows
     int32_t* n_units;
     int unit_rows;
@@ -161,8 +162,8 @@ __device__ void emit_aux(const SortAux& aux, const int32_t* __restrict__ perm, c
         }
         if (aux.shared_gate != nullptr) {
             for (int t = tid; t < aux.n_tokens; t += kSortThreads) {
-                aux.tok_of_slot[A + t] = t;
-                if (aux.w_of_slot) aux.w_of_slot[A + t] = aux.shared_gate[t];
+                aux.tok_of_slot[A + t] = aux.shared_token0 + t;
+                if (aux.w_of_slot) aux.w_of_slot[A + t] = aux.shared_gate[aux.shared_token0 + t];
             }
         }
     }
@@ -308,8 +309,8 @@ sort_small_kernel(const int32_t* __restrict__ ids, int A, int E, int32_t* __rest
     }
     if (aux.tok_of_slot != nullptr && aux.shared_gate != nullptr) {
         for (int t = tid; t < aux.n_tokens; t += kSortThreads) {
-            aux.tok_of_slot[A + t] = t;
-            if (aux.w_of_slot) aux.w_of_slot[A + t] = aux.shared_gate[t];
+            aux.tok_of_slot[A + t] = aux.shared_token0 + t;
+            if (aux.w_of_slot) aux.w_of_slot[A + t] = aux.shared_gate[aux.shared_token0 + t];
         }
     }
     SortAux rest = aux;
@@ -380,8 +381,8 @@ sort_place_kernel(const int32_t* __restrict__ ids, int A, int E, const int32_t* 
         }
     }
     if (aux.tok_of_slot != nullptr && aux.shared_gate != nullptr && i < aux.n_tokens) {
-        aux.tok_of_slot[A + i] = i;
-        if (aux.w_of_slot) aux.w_of_slot[A + i] = aux.shared_gate[i];
+        aux.tok_of_slot[A + i] = aux.shared_token0 + i;
+        if (aux.w_of_slot) aux.w_of_slot[A + i] = aux.shared_gate[aux.shared_token0 + i];
     }
 }
 
@@ -391,7 +392,7 @@ sort_place_kernel(const int32_t* __restrict__ ids, int A, int E, const int32_t* 
 // the positions; also clears the scheduler words.
 static __global__ void __launch_bounds__(kSortThreads)
 build_units_kernel(const int32_t* __restrict__ offsets, int E, int unit_rows, WorkUnit* __restrict__ units,
-                   int32_t* __restrict__ n_units, int32_t* __restrict__ sched) {
+                   int32_t* __restrict__ n_units, int32_t* __restrict__ sched, int extra_from) {
     __shared__ int s_warp[33];
     const int tid = threadIdx.x;
     int cnt = 0, pos0 = 0;
@@ -411,18 +412,18 @@ build_units_kernel(const int32_t* __restrict__ offsets, int E, int unit_rows, Wo
         u.pad = 0;
         units[base + c] = u;
     }
-    if (tid == 0) {
-        n_units[0] = total;
-        n_units[1] = total;          // no extra expert at this entry point: all units are routed
-    }
+    if (tid == 0) n_units[0] = total;
+    // units of the routed experts come first; those of expert `extra_from` (the shared expert, when the caller
+    // lists it as the last "expert") follow
+    if (extra_from >= 0 ? tid == extra_from : tid == 0) n_units[1] = extra_from >= 0 ? base : total;
     if (sched != nullptr)
         for (int i = tid; i < kSchedInts; i += kSortThreads) sched[i] = 0;
 }
 
 int launch_build_units(const int32_t* offsets, int E, int unit_rows, WorkUnit* units, int32_t* n_units,
-                       int32_t* sched, cudaStream_t stream) {
+                       int32_t* sched, cudaStream_t stream, int extra_from) {
     IMX_REQUIRE(E >= 1 && E < kSortThreads, "build_units: num_experts (%d) must be in 1..%d", E, kSortThreads - 1);
-    build_units_kernel<<<1, kSortThreads, 0, stream>>>(offsets, E, unit_rows, units, n_units, sched);
+    build_units_kernel<<<1, kSortThreads, 0, stream>>>(offsets, E, unit_rows, units, n_units, sched, extra_from); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }
@@ -481,6 +482,7 @@ int launch_sort(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offs
         aux.w_of_slot = ex->w_of_slot;
         aux.shared_gate = ex->shared_gate;
         aux.n_tokens = ex->n_tokens;
+        aux.shared_token0 = ex->shared_token0;
         aux.units = ex->units;
         aux.n_units = ex->n_units;
         aux.unit_rows = ex->unit_rows > 0 ? ex->unit_rows : 8;
@@ -489,7 +491,7 @@ int launch_sort(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offs
     }
     const size_t smem_fused = ((size_t)kSortWarps * E + E + E + 1 + 33) * sizeof(int);
     if (A <= kSmallSortIters * kSortThreads && E <= kSmallSortExperts) {
-        sort_small_kernel<<<1, kSortThreads, smem_fused, stream>>>(ids, A, E, counts, offsets, perm, inv_perm, aux);
+        sort_small_kernel<<<1, kSortThreads, smem_fused, stream>>>(ids, A, E, counts, offsets, perm, inv_perm, aux); IMX_LAUNCHED();
         IMX_CHECK_CUDA(cudaGetLastError());
         return IMX_OK;
     }
@@ -497,7 +499,7 @@ int launch_sort(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offs
         IMX_CHECK_CUDA(cudaFuncSetAttribute(sort_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             (int)smem_fused));
         sort_fused_kernel<<<1, kSortThreads, smem_fused, stream>>>(ids, A, E, counts, offsets, perm,
-                                                                   inv_perm, aux);
+                                                                   inv_perm, aux); IMX_LAUNCHED();
         IMX_CHECK_CUDA(cudaGetLastError());
         return IMX_OK;
     }
@@ -508,15 +510,15 @@ int launch_sort(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offs
     const size_t smem_rank = ((size_t)kSortWarps * E + E) * sizeof(int);
     IMX_CHECK_CUDA(cudaFuncSetAttribute(sort_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)smem_rank));
-    sort_rank_kernel<<<nb, kSortThreads, smem_rank, stream>>>(ids, A, E, inv_perm, block_counts);
+    sort_rank_kernel<<<nb, kSortThreads, smem_rank, stream>>>(ids, A, E, inv_perm, block_counts); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     const size_t smem_scan = ((size_t)E + E + 1 + 33) * sizeof(int);
-    sort_scan_kernel<<<1, kSortThreads, smem_scan, stream>>>(block_counts, nb, E, counts, offsets, aux, A);
+    sort_scan_kernel<<<1, kSortThreads, smem_scan, stream>>>(block_counts, nb, E, counts, offsets, aux, A); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     int place_n = A;
     if (aux.tok_of_slot && aux.shared_gate && aux.n_tokens > place_n) place_n = aux.n_tokens;
     sort_place_kernel<<<ceil_div(place_n, 256), 256, 0, stream>>>(ids, A, E, offsets, block_counts, perm,
-                                                                 inv_perm, aux);
+                                                                 inv_perm, aux); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }

@@ -3,6 +3,7 @@
 // device) and the tiled tensor-map encoder with a small cache.
 #include <cuda.h>
 
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -35,6 +36,10 @@ struct MapEntry {
 constexpr int kMapCache = 64;             // per thread: a forward call encodes at most 20 maps
 
 }  // namespace
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 int current_device(DeviceInfo* out) {
     int dev = 0;

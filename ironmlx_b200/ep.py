@@ -46,7 +46,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib, nn, ops
-from ._lib import MoEConfig, check, lib
+from ._lib import MoEConfig, MoEWeights, check, lib
 
 
 class CudaStages:
@@ -151,6 +151,7 @@ class LocalExperts:
     shared_down: Optional[nn.QuantizedLinear] = None      # [1, H, .]
     shared_expert_gate_w: Optional[torch.Tensor] = None
     router_logit_bias: Optional[torch.Tensor] = None
+    shared_mlp: Optional[nn.MLP] = None                   # the same shared expert as three separate projections
 
 
 def fuse_shared(mlp: nn.MLP):
@@ -195,8 +196,9 @@ class ExpertParallelMoE:
                                          _lib.PATH[path])
         self.cfg_routed = mk(intermediate, self.E_loc)
         self.cfg_shared = mk(shared_intermediate, 1) if shared_intermediate else None
-        self.side_stream = (torch.cuda.Stream()
-                            if torch.cuda.is_available() and getattr(weights.router_w, "is_cuda", False) else None)
+        # The routed and the shared expert calls run one after the other on the caller's stream: both are
+        # stream-K launches whose CTAs hand partial sums to one another and must not share the GPU.
+        self.side_stream = None
         self.last = {}
         self._off_cache = {}
         self.gather_limit = 1024         # global tokens up to which the gathered schedule is used
@@ -337,6 +339,86 @@ class ExpertParallelMoE:
         return y
 
 
+class ExpertParallel:
+    """The expert-parallel block behind the C ABI (`imx_ep_*`, csrc/ep.cu): NCCL collectives issued by the
+    library itself on its own communicator, the stage kernels enqueued without Python in between.  One
+    instance per process / GPU; `forward` is collective.
+
+    `weights` holds this rank's block of experts (`LocalExperts`); the communicator's unique id travels from
+    rank 0 through `torch.distributed` (any backend), which is otherwise not used on the data path."""
+
+    def __init__(self, weights: LocalExperts, num_experts: int, top_k: int, norm_topk_prob: bool, hidden: int,
+                 intermediate: int, shared_intermediate: int, group=None, path: str = "auto"):
+        self.w = weights
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        q = weights.gate_up
+        self.cfg = MoEConfig(hidden, num_experts, top_k, intermediate, shared_intermediate, int(norm_topk_prob),
+                             _lib.MODE[q.mode], q.bits, q.group_size, _lib.PATH[path])
+        self.hidden = hidden
+        dev = weights.router_w.device
+        uid = torch.zeros(128, dtype=torch.uint8)
+        if self.rank == 0:
+            buf = (C.c_ubyte * 128)()
+            check(lib().imx_ep_unique_id(buf))
+            uid = torch.tensor(list(buf), dtype=torch.uint8)
+        uid = uid.to(dev) if dist.get_backend(group) == "nccl" else uid
+        dist.broadcast(uid, 0, group=group)
+        raw = bytes(uid.cpu().tolist())
+        self._ctx = C.c_void_p()
+        with torch.cuda.device(dev):
+            check(lib().imx_ep_create(C.byref(self.cfg), raw, self.rank, self.world, C.byref(self._ctx)))
+        self._ws = {}
+        self.info = _lib.EpInfo()
+        self._weights = self._make_weights()
+
+    def _make_weights(self) -> MoEWeights:
+        w, lw = MoEWeights(), self.w
+        w.router_w = lw.router_w.data_ptr()
+        w.router_logit_bias = None if lw.router_logit_bias is None else lw.router_logit_bias.data_ptr()
+        w.gate_up = lw.gate_up.qtensor()
+        w.down = lw.down.qtensor()
+        if lw.shared_mlp is not None:
+            w.shared_gate_proj = lw.shared_mlp.gate_proj.qtensor()
+            w.shared_up_proj = lw.shared_mlp.up_proj.qtensor()
+            w.shared_down_proj = lw.shared_mlp.down_proj.qtensor()
+            w.shared_expert_gate_w = lw.shared_expert_gate_w.data_ptr()
+        return w
+
+    def workspace(self, n_local: int, schedule: str, device) -> torch.Tensor:
+        key = (n_local, schedule)
+        ws = self._ws.get(key)
+        if ws is None:
+            nb = C.c_size_t(0)
+            check(lib().imx_ep_workspace_bytes(self._ctx, n_local, _lib.EP_SCHEDULE[schedule], C.byref(nb)))
+            ws = torch.zeros(nb.value, dtype=torch.uint8, device=device)
+            self._ws[key] = ws
+        return ws
+
+    def forward(self, x: torch.Tensor, schedule: str = "auto", y: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if x.dtype != torch.bfloat16 or not x.is_cuda or x.shape[-1] != self.hidden:
+            raise _lib.IronMLXError(_lib.ERR_INVALID, "ExpertParallel: x must be a bfloat16 CUDA tensor [n, hidden]")
+        x = x.contiguous()
+        n = x.numel() // self.hidden
+        ws = self.workspace(n, schedule, x.device)
+        if y is None:
+            y = torch.empty_like(x)
+        check(lib().imx_ep_forward(self._ctx, C.byref(self._weights), x.data_ptr(), n, y.data_ptr(), ws.data_ptr(),
+                                   ws.numel(), ops.stream_ptr(), _lib.EP_SCHEDULE[schedule], C.byref(self.info)))
+        self._last_ws = ws
+        return y
+
+    def check_status(self) -> None:
+        ws = getattr(self, "_last_ws", None)
+        if ws is not None:
+            check(lib().imx_moe_status(ws.data_ptr(), ops.stream_ptr()))
+
+    def close(self) -> None:
+        if self._ctx:
+            lib().imx_ep_destroy(self._ctx)
+            self._ctx = C.c_void_p()
+
+
 # ── synthetic construction + the benchmark's runner ──────────────────────────
 
 def build_local(cfg, device, rank: int, world: int) -> LocalExperts:
@@ -356,6 +438,7 @@ def build_local(cfg, device, rank: int, world: int) -> LocalExperts:
         mlp = nn.MLP(*(synthetic._single(synthetic._quantize_stack(lambda e, nm=nm: wl.shared(nm), 1, cfg, device))
                        for nm in ("gate_proj", "up_proj", "down_proj")))
         out.shared_gate_up, out.shared_down = fuse_shared(mlp)
+        out.shared_mlp = mlp
         out.shared_expert_gate_w = synthetic._bf16(wl.shared_gate_weight(), device)
     bias = wl.router_logit_bias()
     if bias is not None:
