@@ -1,25 +1,37 @@
 """MoE-layer throughput benchmark.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c2]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--config c2] [--tokens T] [--experts E] [--path auto] [--eager] [--no-prefill]
 
-One step = one pass of the MoE block over one batch of synthetic tokens.
-At N=1 the workload is the Qwen3.5-MoE-shaped decode step (64 tokens, hidden
-2048, 256 experts, top-8, intermediate 512, shared expert, affine 4-bit g64,
-seed 0).  Prints ONE JSON line (rank 0).
+One step = one pass of the MoE block over one batch of synthetic tokens.  Prints
+ONE JSON line (rank 0).
 
-  value     tokens/s with the tokens already resident in HBM (CUDA events
-            around the K timed steps, max over ranks)
-  e2e       tokens/s through the host-buffer entry point: pinned host
-            activations in, pinned host result out, copies inside the timed
-            region
-  roofline  the first expert product (gate/up + SwiGLU), the kernel that moves
-            the most bytes: algorithmic bytes per launch / its average
-            duration from CUDA events recorded around it on its stream
-  cpu_baseline  the CPU restatement of the reference's algorithm timed on this
-            host's cores on a bounded sample (rank 0, N=1 only)
+Headline (`value`): the Qwen3.5-MoE-shaped decode step (c2: 64 tokens, hidden 2048,
+256 experts, top-8, intermediate 512, shared expert, affine 4-bit g64, seed 0); at
+N > 1 every rank brings 64 tokens (weak scaling) and the experts are split over the
+ranks (all-gather + reduce-scatter schedule).
 
---impl reference times that CPU restatement alone (the reference's own MLX
-backend cannot be built here: MLX is not in its tree).
+  value     tokens/s with the tokens already resident in HBM (CUDA events around
+            the K timed steps, max over ranks)
+  e2e       tokens/s with pinned host activations in and a pinned host result out,
+            copies inside the timed region
+  roofline  the first expert product (gate/up + SwiGLU), the kernel that moves the
+            most bytes: algorithmic bytes per launch / its average duration from
+            CUDA events recorded around it on its stream
+  parity    the timed configuration's output against the CPU checker (N = 1) or
+            against the single-GPU block on the same tokens (N > 1)
+  prefill   the same layer on the prefill workload (c3: 8192 tokens, seed 1).
+            N = 1: one GPU, tensor-bound roofline of the tcgen05 gate/up kernel.
+            N > 1: the 8192 tokens sharded evenly, E/N experts per rank, dispatch and
+            combine as NCCL all-to-all; ms/step of the slowest rank, bytes exchanged
+            per rank and the share of the step spent in the two exchanges
+  cpu_baseline  the CPU restatement of the reference's algorithm timed on this host's
+            cores on a bounded sample, before CUDA is initialised (rank 0, N = 1)
+
+--impl reference times that CPU restatement alone, with every host thread, the same
+K and W, and the same global token count (the reference's own MLX backend cannot be
+built here: MLX is not in its tree).  --tokens/--experts/--path/--eager select a
+reduced case and plain launches for profiler captures.
 """
 from __future__ import annotations
 
@@ -35,6 +47,9 @@ sys.path.insert(0, ROOT)
 
 METRIC = "moe_layer_tokens_per_sec"
 UNIT = "tokens/s"
+# DRAM read + write of one launch of the decode gate/up kernel per expert it touches, from the ncu capture of a
+# 97-expert case (118.0 MB, profiles/decode_tmap_kernel_c2.md); each touched expert's bytes are read exactly once
+DECODE_GU_TRAFFIC_PER_EXPERT = 118.0e6 / 97
 
 
 def parse():
@@ -44,9 +59,26 @@ def parse():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2")
+    ap.add_argument("--tokens", type=int, default=0, help="override the configuration's token count")
+    ap.add_argument("--experts", type=int, default=0, help="keep only this many experts")
+    ap.add_argument("--path", default="auto", help="expert-kernel path (auto, decode, prefill, generic)")
+    ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA-graph replay")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill block")
+    ap.add_argument("--prefill-steps", type=int, default=0, help="timed steps of the prefill block (default: min(steps, 50))")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
+
+
+def config_from(args, name=None):
+    from ironmlx_b200.workloads import CONFIGS
+    cfg = CONFIGS[name or args.config]
+    if name is None:
+        if args.experts:
+            cfg = cfg.with_(num_experts=args.experts)
+        if args.tokens:
+            cfg = cfg.with_(tokens=args.tokens)
+    return cfg
 
 
 class ClockSampler:
@@ -111,11 +143,12 @@ class ClockSampler:
 
 
 def peaks():
+    """(HBM GB/s, dense bf16 TFLOP/s burst, source)."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         d = json.load(open(path))
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
 
 
 def workload_desc(cfg, extra=None):
@@ -128,86 +161,90 @@ def workload_desc(cfg, extra=None):
     return d
 
 
-# ── CPU baseline: the checker's restatement of the reference algorithm ───────
-def cpu_baseline(cfg, moe_host_params, x, seconds):
-    """Times the C/OpenMP restatement of the reference's algorithm
-    (oracle/moe_ref.c) on this host's cores on a bounded sample: as many whole
-    steps of the same workload as fit the budget (at least two, first untimed)."""
+# ── the CPU restatement of the reference's algorithm (checker, baseline, reference arm) ──────────────────
+def set_host_threads():
+    """Every host core for the C/OpenMP restatement, whatever the launcher exported (torch.distributed.run
+    sets OMP_NUM_THREADS=1): must run before the library is loaded."""
+    n = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(n)
+    os.environ.pop("OMP_THREAD_LIMIT", None)
+    return n
+
+
+def host_case(cfg, blocks=1):
+    """Checker-side parameters and activations of a configuration (numpy generation and quantization);
+    `blocks` batches of cfg.tokens tokens (one per rank of the repo arm)."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from util import make_params
+    from ironmlx_b200.workloads import Workload
+    x, p = make_params(cfg)
+    if blocks > 1:
+        wl = Workload(cfg)
+        x = np.concatenate([wl.activations(block=b) for b in range(blocks)], 0)
+    return x, p
+
+
+def cpu_sample(cfg, x, p, seconds):
+    """Times the restatement on as many whole steps of the workload as fit the budget (at least two, the first
+    untimed); returns (baseline dict, output of the last step)."""
     from oracle import cref
-    run, _ = cref.prepare(x, moe_host_params)
-    run()                                            # untimed first pass (page-in)
+    run, _ = cref.prepare(x, p)
+    out = run()                                      # untimed first pass (page-in)
     t0 = time.perf_counter()
     steps = 0
     while True:
-        run()
+        out = run()
         steps += 1
         dt = time.perf_counter() - t0
         if dt >= seconds or steps >= 200:
             break
-    return {"value": cfg.tokens * steps / dt, "unit": UNIT, "cores": cref.threads(), "kind": "port",
-            "sample": f"{steps} full step(s) of {cfg.name} in {dt:.1f} s with the C/OpenMP restatement "
-                      f"(per-expert loop, dequantize + fp32 dot products), same packed weights as the GPU"}
-
-
-def host_params_from_device(moe, cfg):
-    """Checker-side parameters holding the very bytes the GPU uses."""
-    import numpy as np
-    from oracle import formats as F
-    from oracle import moe as O
-
-    def q(ql):
-        w = ql.weight.cpu().numpy().view(np.uint32)
-        if ql.mode == "affine":
-            s = ql.scales.view(__import__("torch").int16).cpu().numpy().view(F.bf16)
-            b = ql.biases.view(__import__("torch").int16).cpu().numpy().view(F.bf16)
-        else:
-            s, b = ql.scales.cpu().numpy(), None
-        return O.QLinear(w, s, b, ql.group_size, ql.bits, ql.mode, ql.global_scale)
-
-    import torch
-    p = O.MoEParams(router_w=moe.gate.weight.float().cpu().numpy().astype(F.bf16),
-                    gate_up=q(moe._fused.gate_up), down=q(moe._fused.down),
-                    num_experts_per_tok=cfg.top_k, norm_topk_prob=cfg.norm_topk_prob)
-    if moe.shared_expert is not None:
-        p.shared_gate_proj = q(moe.shared_expert.gate_proj)
-        p.shared_up_proj = q(moe.shared_expert.up_proj)
-        p.shared_down_proj = q(moe.shared_expert.down_proj)
-        p.shared_expert_gate_w = moe.shared_expert_gate.weight.float().cpu().numpy().astype(F.bf16)
-    if moe.router_logit_bias is not None:
-        p.router_logit_bias = moe.router_logit_bias.cpu().numpy()
-    return p
+    return ({"value": x.shape[0] * steps / dt, "unit": UNIT, "cores": cref.threads(), "kind": "port",
+             "sample": f"{steps} full step(s) of {cfg.name} in {dt:.1f} s with the C/OpenMP restatement "
+                       f"(per-expert loop, dequantize + fp32 dot products), before CUDA is initialised"},
+            {k: v.copy() for k, v in out.items()})
 
 
 def run_reference(args):
-    """The reference arm: the CPU restatement of the reference's algorithm on this
-    host's cores (rank 0 only).  The reference's own MLX backend cannot be built:
-    MLX/mlx-c are not in its tree and there is no Rust toolchain."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """The reference arm: the CPU restatement of the reference's algorithm on all of this host's cores, rank 0
+    only, same K and W as the repo arm, same global token count.  The reference's own MLX backend cannot be
+    built: MLX/mlx-c are not in its tree and there is no Rust toolchain."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    from ironmlx_b200.workloads import CONFIGS
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from util import make_params
+    set_host_threads()
     from oracle import cref
-    cfg = CONFIGS[args.config]
-    x, p = make_params(cfg)                          # numpy generation + quantization, untimed
+    cfg = config_from(args)
+    world = max(1, args.gpus)
+    x, p = host_case(cfg, blocks=world)              # untimed
     run, _ = cref.prepare(x, p)
-    warm = max(1, min(args.warmup, 2))
-    for _ in range(warm):
-        run()
-    steps = max(1, min(args.steps, 20))
+    # a step is the whole batch unless K + W full steps would run for more than a few minutes; then every step is
+    # a bounded sample of the batch's tokens
     t0 = time.perf_counter()
-    for _ in range(steps):
+    run()
+    t_full = time.perf_counter() - t0
+    budget = 150.0
+    n_tok = x.shape[0]
+    total = (args.steps + args.warmup) * t_full
+    sample = n_tok if total <= budget else max(1, int(n_tok * budget / total))
+    if sample < n_tok:
+        run, _ = cref.prepare(x[:sample], p)
+    for _ in range(args.warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
         run()
     dt = time.perf_counter() - t0
-    val = cfg.tokens * steps / dt
+    val = sample * args.steps / dt
+    what = (f"{args.steps} full step(s) of {n_tok} tokens" if sample == n_tok else
+            f"{args.steps} step(s) on the first {sample} of {n_tok} tokens (bounded sample)")
     line = {
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": warm, "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_desc(cfg),
+        "config": workload_desc(cfg, {"parallelism": f"ep{world}" if world > 1 else "single",
+                                      "launch": "the step's kernels replayed as one CUDA graph"}),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cref.threads(), "kind": "port",
-                         "sample": f"{steps} full step(s) of {cfg.name} with the C/OpenMP restatement"},
+                         "sample": what + f" of {cfg.name} with the C/OpenMP restatement"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference's MLX backend is not buildable here (MLX absent from its tree, no Rust toolchain); "
                 "this is the C/OpenMP restatement of its algorithm (oracle/moe_ref.c)",
@@ -215,160 +252,372 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+# ── GPU side ─────────────────────────────────────────────────────────────────────────────────────────────
+def timed_steps(step, steps, warmup, barrier, dev, world, sampler_index):
+    """W untimed + K timed calls of `step` between barriers; CUDA events; max over ranks -> (ms/step, clocks)."""
+    import torch
+    import torch.distributed as dist
+    for _ in range(max(warmup, 3)):
+        step()
+    barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(sampler_index) as clocks:
+        barrier()
+        start.record()
+        for _ in range(steps):
+            step()
+        end.record()
+        barrier()
+    t = torch.tensor([start.elapsed_time(end) / steps], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item()), clocks.summary()
+
+
+def wall_steps(step, steps, barrier, dev, world):
+    """Host-clock time per call of a `step` that synchronises itself (end-to-end numbers), max over ranks."""
+    import torch
+    import torch.distributed as dist
+    for _ in range(3):
+        step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    t = torch.tensor([(time.perf_counter() - t0) / steps * 1e3], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def rel_l2(a, b):
+    import numpy as np
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def single_gpu(args, dev, barrier):
+    import numpy as np
+    import torch
+    from ironmlx_b200 import synthetic, _lib
+    from ironmlx_b200.workloads import Workload, algorithmic_bytes_decode, algorithmic_flops
+
+    cfg = config_from(args)
+    hbm_peak, tf_peak, which = peaks()
+    lib = _lib.lib()
+
+    def measure(cfg, steps, path):
+        """Device-resident and end-to-end timing of one configuration on this GPU, stage times, launches."""
+        moe = synthetic.build_moe(cfg, dev, path=path)
+        x = torch.from_numpy(Workload(cfg).activations()).to(dev).to(torch.bfloat16)
+        torch.cuda.synchronize()
+        out = {}
+        if args.eager:
+            y_box = [None]
+
+            def step():
+                y_box[0] = moe.forward_with_stream(x)
+            c0 = lib.imx_launch_count()
+            step()
+            out["launches_per_step"] = int(lib.imx_launch_count() - c0)
+            get_y = lambda: y_box[0]
+        else:
+            c0 = lib.imx_launch_count()
+            captured = moe.capture(x)                # the step's kernels as one CUDA graph on static buffers
+            out["launches_per_step"] = int(lib.imx_launch_count() - c0) // 3     # two warm-up passes + the capture
+            step = lambda: captured()
+            get_y = lambda: captured.y
+        ms, clocks = timed_steps(step, steps, args.warmup, barrier, dev, 1, dev.index or 0)
+        out.update(ms=ms, clocks=clocks)
+        # end to end: pinned host activations in, pinned host result out, copies inside the timed region
+        xh = x.cpu().pin_memory()
+        yh = torch.empty_like(xh).pin_memory()
+        if args.eager:
+            e2e_step = lambda: moe.forward_host(xh, yh)
+        else:
+            e2e_step = moe.capture(x, xh, yh).run_host      # copy in, block, copy out as one graph; sync per step
+        out["e2e_ms"] = wall_steps(e2e_step, max(10, steps // 10), barrier, dev, 1)
+        stage = np.zeros(5)
+        reps = 30
+        for _ in range(reps):
+            _, st = moe.forward_timed(x)
+            stage += np.array(st)
+        out["stage"] = stage / reps
+        y, tr = moe.forward_with_stream(x, trace=True)
+        torch.cuda.synchronize()
+        moe.check_status()                            # a bounded wait that ran out would leave its mark here
+        out.update(y=y.float().cpu().numpy(), counts=tr["counts"].cpu().numpy(), step_y=get_y().float().cpu().numpy())
+        return out
+
+    m = measure(cfg, args.steps, args.path)
+    stage = m["stage"]
+    stage_ms = {"router": float(stage[0]), "sort": float(stage[1]), "gate_up": float(stage[2]),
+                "down": float(stage[3]), "combine": float(stage[4])}
+    io_bytes = cfg.tokens * cfg.hidden * 2
+    line = {
+        "metric": METRIC, "value": cfg.tokens / (m["ms"] * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": m["ms"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+        "config": workload_desc(cfg, {"parallelism": "single",
+                                      "launch": "plain launches" if args.eager else "the step's kernels replayed as one CUDA graph"}),
+        "e2e": {"value": cfg.tokens / (m["e2e_ms"] * 1e-3), "unit": UNIT, "h2d_bytes_per_step": io_bytes,
+                "d2h_bytes_per_step": io_bytes, "ms_per_step": m["e2e_ms"]},
+        "clocks": m["clocks"],
+        "gpu_launches": m["launches_per_step"] * args.steps,
+        "gpu_launches_note": f"{m['launches_per_step']} kernels of this library per step, counted by the library "
+                             "(imx_launch_count) while the step was recorded",
+    }
+    touched = int((m["counts"] > 0).sum())
+    per_w = {"affine": cfg.bits / 8 + 4 / cfg.group_size, "mxfp8": 1 + 1 / 32, "nvfp4": 0.5 + 1 / 16}[cfg.mode]
+    prefill_like = cfg.tokens * cfg.top_k >= 32 * cfg.num_experts
+    if not prefill_like:
+        gu_bytes = (touched * 2 * cfg.intermediate + 2 * cfg.shared_intermediate) * cfg.hidden * per_w
+        achieved = gu_bytes / (stage[2] * 1e-3) / 1e9
+        total_bytes = algorithmic_bytes_decode(cfg, touched)
+        tmap = cfg.mode == "affine" and cfg.bits == 4 and cfg.group_size == 64
+        line["roofline"] = {
+            "bound": "hbm", "kernel": "decode_tmap_kernel<true> (gate/up + SwiGLU)" if tmap else "decode kernel, first product",
+            "achieved": achieved, "peak": hbm_peak, "peak_source": f"of {which}", "unit": "GB/s", "frac": achieved / hbm_peak,
+            "traffic": DECODE_GU_TRAFFIC_PER_EXPERT * (touched + 1) if tmap and cfg.name == "c2" else None,
+            "traffic_note": "dram read + write per touched expert from the ncu capture of a 97-expert case "
+                            "(profiles/decode_tmap_kernel_c2.md), times the experts this launch touches: each expert's "
+                            "bytes are read once, so traffic grows in proportion",
+            "algorithmic_bytes_per_launch": gu_bytes, "launch_ms": float(stage[2]), "stage_ms": stage_ms,
+            "layer": {"algorithmic_bytes": total_bytes, "touched_experts": touched,
+                      "achieved_gbs": total_bytes / (m["ms"] * 1e-3) / 1e9,
+                      "frac": total_bytes / (m["ms"] * 1e-3) / 1e9 / hbm_peak},
+        }
+    else:
+        line["roofline"] = tensor_roofline(cfg, stage, stage_ms, m["ms"], tf_peak, which)
+    line["_y"] = m["step_y"]
+    line["_cfg"] = cfg
+
+    if not args.no_prefill and not prefill_like and args.config == "c2" and not (args.tokens or args.experts):
+        torch.cuda.empty_cache()
+        pcfg = config_from(args, "c3")
+        psteps = args.prefill_steps or min(args.steps, 50)
+        pm = measure(pcfg, psteps, "auto")
+        pst = pm["stage"]
+        pstage_ms = {"router": float(pst[0]), "sort": float(pst[1]), "gate_up": float(pst[2]),
+                     "down": float(pst[3]), "combine": float(pst[4])}
+        pio = pcfg.tokens * pcfg.hidden * 2
+        line["prefill"] = {
+            "config": workload_desc(pcfg, {"parallelism": "single"}), "steps": psteps,
+            "ms_per_step": pm["ms"], "value": pcfg.tokens / (pm["ms"] * 1e-3), "unit": UNIT,
+            "e2e": {"value": pcfg.tokens / (pm["e2e_ms"] * 1e-3), "unit": UNIT, "h2d_bytes_per_step": pio,
+                    "d2h_bytes_per_step": pio, "ms_per_step": pm["e2e_ms"]},
+            "roofline": tensor_roofline(pcfg, pst, pstage_ms, pm["ms"], tf_peak, which),
+            "clocks": pm["clocks"], "gpu_launches": pm["launches_per_step"] * psteps,
+        }
+    return line
+
+
+def tensor_roofline(cfg, stage, stage_ms, ms, tf_peak, which):
+    from ironmlx_b200.workloads import algorithmic_flops
+    gu_flops = 4 * cfg.tokens * cfg.hidden * (cfg.top_k * cfg.intermediate + cfg.shared_intermediate)
+    achieved = gu_flops / (stage[2] * 1e-3) / 1e12
+    total_flops = algorithmic_flops(cfg)
+    return {
+        "bound": "tensor", "kernel": "prefill_tc_kernel<SwiGLU> (gate/up + SwiGLU, tcgen05, A operand in tensor memory)",
+        "achieved": achieved, "peak": tf_peak, "peak_source": f"of {which} (bf16 burst)", "unit": "TFLOP/s",
+        "frac": achieved / tf_peak, "traffic": None, "algorithmic_flops_per_launch": gu_flops,
+        "launch_ms": float(stage[2]), "stage_ms": stage_ms,
+        "layer": {"algorithmic_flops": total_flops, "achieved_tflops": total_flops / (ms * 1e-3) / 1e12,
+                  "frac": total_flops / (ms * 1e-3) / 1e12 / tf_peak},
+    }
+
+
+def multi_gpu(args, dev, rank, world, barrier):
+    """N > 1: the experts split over the ranks (C-ABI expert-parallel layer, NCCL)."""
+    import numpy as np
+    import torch
+    from ironmlx_b200 import _lib, ep, synthetic
+    from ironmlx_b200.workloads import Workload
+
+    cfg = config_from(args)
+    lib = _lib.lib()
+    _, tf_peak, which = peaks()
+
+    def build(cfg, n_local):
+        moe = ep.ExpertParallel(ep.build_local(cfg, dev, rank, world), cfg.num_experts, cfg.top_k, cfg.norm_topk_prob,
+                                cfg.hidden, cfg.intermediate, cfg.shared_intermediate)
+        return moe
+
+    # ---- headline: decode step, cfg.tokens tokens per rank, gathered schedule replayed as one CUDA graph ----
+    moe = build(cfg, cfg.tokens)
+    x = torch.from_numpy(Workload(cfg).activations(block=rank)).to(dev).to(torch.bfloat16)
+    xd, y = x.clone(), torch.empty_like(x)
+    for _ in range(3):
+        moe.forward(xd, "gathered", y)
+    torch.cuda.synchronize()
+    graph = None
+    launches = None
+    if not args.eager:
+        try:
+            g = torch.cuda.CUDAGraph()
+            c0 = lib.imx_launch_count()
+            with torch.cuda.graph(g):
+                moe.forward(xd, "gathered", y)
+            launches = int(lib.imx_launch_count() - c0)
+            graph = g
+        except Exception as e:                       # capture not possible on this stack: plain launches
+            graph = None
+            torch.cuda.synchronize()
+    if launches is None:
+        c0 = lib.imx_launch_count()
+        moe.forward(xd, "gathered", y)
+        launches = int(lib.imx_launch_count() - c0)
+    step = (lambda: graph.replay()) if graph is not None else (lambda: moe.forward(xd, "gathered", y))
+    ms, clocks = timed_steps(step, args.steps, args.warmup, barrier, dev, world, dev.index or 0)
+    xh, yh = x.cpu().pin_memory(), torch.empty_like(x).cpu().pin_memory()
+
+    def e2e_step():
+        xd.copy_(xh, non_blocking=True)
+        step()
+        yh.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e2e_ms = wall_steps(e2e_step, max(10, args.steps // 10), barrier, dev, world)
+    torch.cuda.synchronize()
+    moe.check_status()
+    y_timed = y.clone()
+    info = {"schedule": int(moe.info.schedule), "bytes_sent": int(moe.info.bytes_sent)}
+
+    # ---- parity of what was timed: rank 0 against the single-GPU block on its own tokens (untimed) ----
+    parity = None
+    y_a2a, tr_a2a = None, None
+    a2a_ok = True
+    try:
+        y_a2a, tr_a2a = moe.forward(xd, "a2a", trace=True)   # the other schedule on the same tokens
+        torch.cuda.synchronize()
+    except _lib.IronMLXError:
+        a2a_ok = False
+    if rank == 0:
+        full = synthetic.build_moe(cfg, dev)
+        y1, tr1 = full.forward_with_stream(x, trace=True)
+        torch.cuda.synchronize()
+        parity = {"rel_l2_vs_single_gpu": rel_l2(y_timed.float().cpu().numpy(), y1.float().cpu().numpy()),
+                  "schedule": "gathered"}
+        if a2a_ok:
+            parity["perm_bit_exact"] = bool(torch.equal(tr_a2a["perm"], tr1["perm"]) and
+                                            torch.equal(tr_a2a["topk_idx"], tr1["topk_idx"]))
+            parity["all_to_all_rel_l2_vs_single_gpu"] = rel_l2(y_a2a.float().cpu().numpy(), y1.float().cpu().numpy())
+        del full
+    moe.close()
+    del moe
+    torch.cuda.empty_cache()
+
+    tokens_per_step = cfg.tokens * world
+    io_bytes = cfg.tokens * cfg.hidden * 2
+    line = {
+        "metric": METRIC, "value": tokens_per_step / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+        "config": workload_desc(cfg, {"parallelism": f"ep{world}",
+                                      "launch": "the step's kernels replayed as one CUDA graph" if graph is not None else "plain launches"}),
+        "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": io_bytes,
+                "d2h_bytes_per_step": io_bytes, "ms_per_step": e2e_ms},
+        "clocks": clocks,
+        "gpu_launches": launches * args.steps,
+        "gpu_launches_note": f"{launches} kernels of this library per step and rank (imx_launch_count), plus NCCL's two collectives",
+        "parity": parity,
+        "ep": {"experts_per_rank": cfg.num_experts // world, "tokens_per_rank": cfg.tokens,
+               "schedule": "gathered: NCCL all-gather of the tokens + reduce-scatter of fp32 partial rows, issued by the library",
+               "bytes_per_rank_per_step": info["bytes_sent"], "cuda_graph": graph is not None},
+    }
+
+    # ---- prefill block: c3's 8192 tokens sharded evenly, all-to-all schedule ----
+    if not args.no_prefill and args.config == "c2" and not (args.tokens or args.experts):
+        pcfg = config_from(args, "c3")
+        n_loc = pcfg.tokens // world
+        pmoe = build(pcfg, n_loc)
+        px = torch.from_numpy(Workload(pcfg).activations()[rank * n_loc:(rank + 1) * n_loc]).to(dev).to(torch.bfloat16)
+        py = torch.empty_like(px)
+        psteps = args.prefill_steps or min(args.steps, 50)
+        pms, pclocks = timed_steps(lambda: pmoe.forward(px, "a2a", py), psteps, args.warmup, barrier, dev, world, dev.index or 0)
+        phases = np.zeros(5)
+        reps = 10
+        for _ in range(reps):
+            pmoe.forward(px, "a2a", py, timed=True)
+            phases += np.array(list(pmoe.info.phase_ms))
+        phases /= reps
+        torch.cuda.synchronize()
+        pmoe.check_status()
+        t = torch.tensor(list(phases) + [float(pmoe.info.bytes_sent), float(pmoe.info.rows_received)], device=dev, dtype=torch.float64)
+        import torch.distributed as dist
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        ph = tmax[:5].tolist()
+        # parity: rank 0's rows against the single-GPU block on the same tokens
+        pparity = None
+        if rank == 0:
+            full = synthetic.build_moe(pcfg, dev)
+            y1 = full.forward_with_stream(px)
+            torch.cuda.synchronize()
+            pparity = {"rel_l2_vs_single_gpu": rel_l2(py.float().cpu().numpy(), y1.float().cpu().numpy()),
+                       "bit_identical": bool(torch.equal(py, y1))}
+            del full
+        from ironmlx_b200.workloads import algorithmic_flops
+        flops = algorithmic_flops(pcfg)
+        line["prefill"] = {
+            "config": workload_desc(pcfg, {"parallelism": f"ep{world}: {n_loc} tokens and {pcfg.num_experts // world} experts per rank"}),
+            "steps": psteps, "ms_per_step": pms, "value": pcfg.tokens / (pms * 1e-3), "unit": UNIT, "scaling": "strong",
+            "phase_ms_slowest_rank": {"route_sort_pack": ph[0], "dispatch": ph[1], "experts": ph[2], "return": ph[3], "combine": ph[4]},
+            "exchange_share_of_step": (ph[1] + ph[3]) / max(sum(ph), 1e-9),
+            "bytes_exchanged_per_rank_per_step": int(tmax[5].item()), "rows_on_busiest_rank": int(tmax[6].item()),
+            "achieved_tflops": flops / (pms * 1e-3) / 1e12, "frac_of_n_gpu_peak": flops / (pms * 1e-3) / 1e12 / (tf_peak * world),
+            "peak_source": f"of {which} (bf16 burst, x{world})", "clocks": pclocks, "parity": pparity,
+            "exchange": "NCCL grouped ncclSend/ncclRecv of fp16 rows each way + an all-gather of the [E] counts (one host synchronisation)",
+        }
+        pmoe.close()
+    return line
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference(args)
         return
-    import numpy as np
-    import torch
-    import torch.distributed as dist
-
-    from ironmlx_b200 import synthetic
-    from ironmlx_b200.workloads import CONFIGS, Workload, algorithmic_bytes_decode
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    # the CPU baseline first: nothing of CUDA, NVML or the sampler thread is alive yet
+    baseline, checker_y = None, None
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        set_host_threads()
+        cfg = config_from(args)
+        xh, ph = host_case(cfg)
+        baseline, out = cpu_sample(cfg, xh, ph, args.cpu_seconds)
+        checker_y = out["y"]
+
+    import torch
+    import torch.distributed as dist
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    cfg = CONFIGS[args.config]
-    wl = Workload(cfg)
-
-    if world > 1:
-        from ironmlx_b200 import ep
-        runner = ep.build_bench_runner(cfg, dev, rank, world)
-    else:
-        moe = synthetic.build_moe(cfg, dev)
-        x = torch.from_numpy(wl.activations()).to(dev).to(torch.bfloat16)
-        runner = None
-    torch.cuda.synchronize()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident throughput ----
-    if runner is None:
-        captured = moe.capture(x)                # the step's kernels as one CUDA graph on static buffers
-        step = lambda: captured()
-    else:
-        step = runner.step
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
-        barrier()
-        start.record()
-        for _ in range(args.steps):
-            step()
-        end.record()
-        barrier()
-    ms = start.elapsed_time(end) / args.steps
-    t = torch.tensor([ms], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    tokens_per_step = cfg.tokens * world
-    value = tokens_per_step / (ms * 1e-3)
-
-    # ---- end to end through the host-buffer entry point ----
-    if runner is None:
-        xh = x.cpu().pin_memory()
-        yh = torch.empty_like(xh).pin_memory()
-        captured_host = moe.capture(x, xh, yh)   # copy in, block, copy out as one graph; sync per step
-        e2e_step = captured_host.run_host
-    else:
-        e2e_step = runner.step_host
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    e2e_steps = max(10, args.steps // 10)
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
-    t = torch.tensor([e2e_ms], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item())
-    io_bytes = cfg.tokens * cfg.hidden * 2
-
-    line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
-        "config": workload_desc(cfg, {"parallelism": f"ep{world}" if world > 1 else "single",
-                                      "launch": "the step's kernels replayed as one CUDA graph"}),
-        "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": io_bytes,
-                "d2h_bytes_per_step": io_bytes, "ms_per_step": e2e_ms},
-        "clocks": clocks.summary(),
-    }
-
-    if runner is None:
-        # ---- roofline of the dominant kernel, timed live with CUDA events ----
-        stage = np.zeros(5)
-        reps = 50
-        for _ in range(reps):
-            _, st = moe.forward_timed(x)
-            stage += np.array(st)
-        stage /= reps
-        _, tr = moe.forward_with_stream(x, trace=True)
-        touched = int((tr["counts"] > 0).sum().item())
-        per_w = cfg.bits / 8 + 4 / cfg.group_size if cfg.mode == "affine" else (1 + 1 / 32 if cfg.mode == "mxfp8" else 0.5 + 1 / 16)
-        gu_bytes = (touched * 2 * cfg.intermediate + 2 * cfg.shared_intermediate) * cfg.hidden * per_w
-        peak, which = peaks()
-        stage_ms = {"router": float(stage[0]), "sort": float(stage[1]), "gate_up": float(stage[2]),
-                    "down": float(stage[3]), "combine": float(stage[4])}
-        prefill = cfg.tokens * cfg.top_k >= 32 * cfg.num_experts and cfg.mode == "affine" and cfg.bits == 4
-        if not prefill:
-            achieved = gu_bytes / (stage[2] * 1e-3) / 1e9
-            total_bytes = algorithmic_bytes_decode(cfg, touched)
-            line["roofline"] = {
-                "bound": "hbm", "kernel": "decode_tmap_kernel<true> (gate/up + SwiGLU)", "achieved": achieved,
-                "peak": peak, "peak_source": f"of {which}", "unit": "GB/s", "frac": achieved / peak,
-                "traffic": 265.1e6 if cfg.name == "c2" else None,
-                "traffic_note": "dram read+write per launch from the ncu capture of a 97-expert case, scaled by touched experts "
-                                "(profiles/decode_tmap_kernel_c2.md): the algorithmic bytes plus the SwiGLU rows written",
-                "algorithmic_bytes_per_launch": gu_bytes, "launch_ms": float(stage[2]), "stage_ms": stage_ms,
-                "layer": {"algorithmic_bytes": total_bytes, "touched_experts": touched,
-                          "achieved_gbs": total_bytes / (ms * 1e-3) / 1e9, "frac": total_bytes / (ms * 1e-3) / 1e9 / peak},
-            }
-        else:
-            # tensor-core bound: dense-equivalent flops of the first expert product / its duration
-            tf_peak = 1590.0
-            pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
-            if os.path.exists(pk):
-                tf_peak = float(json.load(open(pk))["bf16_tflops"])
-            from ironmlx_b200.workloads import algorithmic_flops
-            gu_flops = 4 * cfg.tokens * cfg.hidden * (cfg.top_k * cfg.intermediate + cfg.shared_intermediate)
-            achieved = gu_flops / (stage[2] * 1e-3) / 1e12
-            total_flops = algorithmic_flops(cfg)
-            line["roofline"] = {
-                "bound": "tensor", "kernel": "prefill_umma_kernel<true> (gate/up + SwiGLU, tcgen05)", "achieved": achieved,
-                "peak": tf_peak, "peak_source": f"of {which} (bf16 burst)", "unit": "TFLOP/s", "frac": achieved / tf_peak,
-                "traffic": None, "algorithmic_flops_per_launch": gu_flops, "launch_ms": float(stage[2]),
-                "stage_ms": stage_ms,
-                "layer": {"algorithmic_flops": total_flops, "achieved_tflops": total_flops / (ms * 1e-3) / 1e12,
-                          "frac": total_flops / (ms * 1e-3) / 1e12 / tf_peak},
-            }
-        line["gpu_launches"] = (8 if prefill else 6) * args.steps      # decode: router x2, sort, 2 products, combine
-        if rank == 0 and not args.no_cpu_baseline:
-            p = host_params_from_device(moe, cfg)
-            xs = wl.activations()
-            line["cpu_baseline"] = cpu_baseline(cfg, p, xs, args.cpu_seconds)
-    else:
-        line["gpu_launches"] = runner.launches_per_step * args.steps
-        line.update(runner.extra())
+    line = single_gpu(args, dev, barrier) if world == 1 else multi_gpu(args, dev, rank, world, barrier)
+    y_step = line.pop("_y", None)
+    line.pop("_cfg", None)
+    if baseline is not None:
+        line["cpu_baseline"] = baseline
+        # the timed step's own output against the checker (same seeded inputs, same packed weights)
+        err = rel_l2(y_step, checker_y)
+        line["parity"] = {"rel_l2_vs_checker": err, "tolerance": 2e-3, "ok": bool(err <= 2e-3)}
+        if err > 2e-3:
+            print(json.dumps(line), flush=True)
+            raise SystemExit(f"bench: the timed step's output is {err:.3e} from the checker (tolerance 2e-3)")
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
-        # Leave without tearing the communicator down: destroying NCCL while captured CUDA graphs
+        # Leave without tearing the communicators down: destroying NCCL while captured CUDA graphs
         # that contain its collectives are still alive can block.  Every rank is past its last
         # collective here (barrier), nothing is in flight (synchronize).
         dist.barrier()

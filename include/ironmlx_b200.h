@@ -286,10 +286,13 @@ typedef struct imx_ep_ctx imx_ep_ctx;
                                 imx_moe_forward on one GPU; needs a format/shape the tensor-core kernels take */
 
 typedef struct imx_ep_info {
+    int want_timing;                     /* IN: non-zero = all-to-all: record and report phase_ms (synchronises) */
     int schedule;                        /* the schedule that ran                          */
     long long rows_received;             /* all-to-all: rows this rank's experts processed */
     unsigned long long bytes_sent;       /* bytes this rank put on the wire in the call    */
     unsigned long long bytes_received;
+    float phase_ms[5];                   /* all-to-all with want_timing: local route/sort/pack, dispatch (count
+                                            exchange, host round trip, rows), experts, return, combine */
 } imx_ep_info;
 
 /* An NCCL unique id (rank 0 makes one and hands it to the others by whatever means the host has). */
@@ -304,9 +307,11 @@ IMX_API int imx_ep_destroy(imx_ep_ctx* ctx);
 IMX_API int imx_ep_workspace_bytes(const imx_ep_ctx* ctx, int n_local, int schedule, size_t* bytes);
 /* y[n_local, H] = MoE(x[n_local, H]) with the experts spread over the ranks.  Collective: every rank calls it
  * with the same n_local and schedule.  workspace: zero-filled once, 256-byte aligned; imx_moe_status() reads its
- * status word.  info may be NULL. */
+ * status word.  info and trace may be NULL; trace (all-to-all schedule only) receives the local tokens' routing and
+ * their dispatch permutation over the global expert ids, as imx_moe_forward would report them. */
 IMX_API int imx_ep_forward(imx_ep_ctx* ctx, const imx_moe_weights* local_weights, const void* x, int n_local, void* y,
-                   void* workspace, size_t workspace_bytes, void* stream, int schedule, imx_ep_info* info);
+                   void* workspace, size_t workspace_bytes, void* stream, int schedule, imx_ep_info* info,
+                   const imx_moe_trace* trace);
 
 /* ── the reference's quantized-op surface, mlx/src/ops.rs:630-727 ──────── */
 

@@ -39,8 +39,8 @@ class MoEWeights(C.Structure):
 
 
 class EpInfo(C.Structure):
-    _fields_ = [("schedule", C.c_int), ("rows_received", C.c_longlong), ("bytes_sent", C.c_ulonglong),
-                ("bytes_received", C.c_ulonglong)]
+    _fields_ = [("want_timing", C.c_int), ("schedule", C.c_int), ("rows_received", C.c_longlong),
+                ("bytes_sent", C.c_ulonglong), ("bytes_received", C.c_ulonglong), ("phase_ms", C.c_float * 5)]
 
 
 EP_SCHEDULE = {"auto": 0, "gathered": 1, "a2a": 2}
@@ -85,7 +85,8 @@ SIGNATURES = {
     "imx_ep_create_from_comm": (_i, [C.POINTER(MoEConfig), _vp, _i, _i, C.POINTER(_vp)]),
     "imx_ep_destroy": (_i, [_vp]),
     "imx_ep_workspace_bytes": (_i, [_vp, _i, _i, C.POINTER(_sz)]),
-    "imx_ep_forward": (_i, [_vp, C.POINTER(MoEWeights), _vp, _i, _vp, _vp, _sz, _vp, _i, C.POINTER(EpInfo)]),
+    "imx_ep_forward": (_i, [_vp, C.POINTER(MoEWeights), _vp, _i, _vp, _vp, _sz, _vp, _i, C.POINTER(EpInfo),
+                            C.POINTER(MoETrace)]),
     "imx_dequantize": (_i, [C.POINTER(QTensor), _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "imx_quantized_matmul": (_i, [_vp, _i, C.POINTER(QTensor), _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "imx_quantize": (_i, [_vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp]),

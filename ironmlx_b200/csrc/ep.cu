@@ -49,6 +49,8 @@ struct imx_ep_ctx {
     bool own_comm;
     int32_t* host_counts;      // pinned [world * E]
     std::vector<size_t> send_rows, recv_rows;
+    cudaEvent_t ev[6];         // phase boundaries of a timed all-to-all call
+    bool have_events;
 };
 
 namespace imx {
@@ -428,7 +430,7 @@ int forward_gathered(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, i
 }
 
 int forward_a2a(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, int n, void* y, void* workspace, size_t ws_bytes,
-                cudaStream_t stream, imx_ep_info* info) {
+                cudaStream_t stream, imx_ep_info* info, const imx_moe_trace* trace) {
     const NcclApi* nc = nccl_api();
     const imx_moe_config& c = x.cfg;
     QFormat f;
@@ -449,6 +451,13 @@ int forward_a2a(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, int n,
     const int path = IMX_PATH_PREFILL;
     int order[16];
     path_block_order(path, f, order);
+    const bool timed = info != nullptr && info->want_timing != 0;
+    if (timed && !x.have_events) {
+        for (int i = 0; i < 6; ++i) IMX_CHECK_CUDA(cudaEventCreate(&x.ev[i]));
+        x.have_events = true;
+    }
+    auto mark = [&](int i) -> cudaError_t { return timed ? cudaEventRecord(x.ev[i], stream) : cudaSuccess; };
+    IMX_CHECK_CUDA(mark(0));
 
     // 1. route the local tokens; their fp16 rows land behind the receive buffer's `cap` rows, where the shared
     //    expert's slots will find them
@@ -466,6 +475,7 @@ int forward_a2a(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, int n,
     IMX_TRY(launch_sort(ws.topk_idx, A, E, ws.counts, ws.offsets, ws.perm, ws.inv_perm, ws.sort_scratch, ws.sort_scratch_bytes,
                         &ex, stream));
     IMX_TRY(launch_gather_rows(x16, ws.tok_of_slot, A, (size_t)H * 2, ws.send_buf, stream));
+    IMX_CHECK_CUDA(mark(1));
     // 3. everyone's counts; the split sizes are host values: the one synchronisation of the step
     IMX_CHECK_NCCL(nc->AllGather(ws.counts, ws.all_counts, (size_t)E, ncclInt32, x.comm, stream));
     IMX_CHECK_CUDA(cudaMemcpyAsync(x.host_counts, ws.all_counts, sizeof(int32_t) * R * E, cudaMemcpyDeviceToHost, stream));
@@ -507,6 +517,7 @@ int forward_a2a(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, int n,
             IMX_CHECK_CUDA(cudaMemcpyAsync(ws.recv_buf + ro * H, ws.send_buf + so * H, x.send_rows[x.rank] * H * 2,
                                            cudaMemcpyDeviceToDevice, stream));
     }
+    IMX_CHECK_CUDA(mark(2));
     // 5. expert-major view of the received rows (+ the shared expert's slots), unit list
     ep_regroup_kernel<<<x.e_loc + 1, 256, 0, stream>>>(ws.all_counts, R, E, x.rank * x.e_loc, x.e_loc, ws.cap, n, has_shared ? 1 : 0,
                                                      ws.row_index, ws.offsets2); IMX_LAUNCHED();
@@ -534,6 +545,7 @@ int forward_a2a(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, int n,
     ga.out_index = ws.row_index;
     ga.status = ws.c.status;
     if (ga.n_slots > 0) IMX_TRY(run_experts(path, ga, stream));
+    IMX_CHECK_CUDA(mark(3));
     // 7. the rows travel back: what came from rank p returns to rank p, into this rank's sorted slot order
     {
         size_t so = 0, ro = 0;
@@ -553,10 +565,29 @@ int forward_a2a(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, int n,
             IMX_CHECK_CUDA(cudaMemcpyAsync(ws.rows_back + so * H, ws.ret_buf + ro * H, x.send_rows[x.rank] * H * 2,
                                            cudaMemcpyDeviceToDevice, stream));
     }
+    IMX_CHECK_CUDA(mark(4));
     // 8. weighted combine on the source rank, ascending slot order; the shared rows sit behind the received ones
     IMX_TRY(launch_combine(ws.rows_back, ws.w_of_slot, ws.inv_perm, n, c.top_k, H,
                            has_shared ? ws.ret_buf + (size_t)ws.cap * H : nullptr, y, stream, false, nullptr, true,
                            has_shared ? ws.shared_gate : nullptr));
+    IMX_CHECK_CUDA(mark(5));
+    if (trace != nullptr) {
+        auto cp = [&](void* dst, const void* src, size_t bytes) -> cudaError_t {
+            return dst ? cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream) : cudaSuccess;
+        };
+        IMX_CHECK_CUDA(cp(trace->topk_idx, ws.topk_idx, (size_t)A * 4));
+        IMX_CHECK_CUDA(cp(trace->topk_w, ws.topk_w, (size_t)A * 4));
+        IMX_CHECK_CUDA(cp(trace->counts, ws.counts, (size_t)E * 4));
+        IMX_CHECK_CUDA(cp(trace->offsets, ws.offsets, (size_t)(E + 1) * 4));
+        IMX_CHECK_CUDA(cp(trace->perm, ws.perm, (size_t)A * 4));
+        IMX_CHECK_CUDA(cp(trace->inv_perm, ws.inv_perm, (size_t)A * 4));
+        if (has_shared) IMX_CHECK_CUDA(cp(trace->shared_gate, ws.shared_gate, (size_t)n * 4));
+    }
+    if (timed) {
+        // local preparation, dispatch (count exchange, host round trip, rows), experts, return, combine
+        IMX_CHECK_CUDA(cudaEventSynchronize(x.ev[5]));
+        for (int i = 0; i < 5; ++i) IMX_CHECK_CUDA(cudaEventElapsedTime(&info->phase_ms[i], x.ev[i], x.ev[i + 1]));
+    }
     if (info != nullptr) {
         info->schedule = IMX_EP_ALL_TO_ALL;
         info->rows_received = (long long)n_recv;
@@ -609,6 +640,7 @@ static int ep_new(const imx_moe_config* cfg, int rank, int world, imx_ep_ctx** o
     x->host_counts = nullptr;
     x->send_rows.assign(world, 0);
     x->recv_rows.assign(world, 0);
+    x->have_events = false;
     if (cudaGetDevice(&x->device) != cudaSuccess ||
         cudaMallocHost((void**)&x->host_counts, sizeof(int32_t) * (size_t)world * cfg->num_experts) != cudaSuccess) {
         set_error("ep_create: pinned host buffer for the count matrix could not be allocated");
@@ -654,6 +686,8 @@ int imx_ep_destroy(imx_ep_ctx* x) {
     const NcclApi* nc = nccl_api();
     if (x->own_comm && x->comm != nullptr && nc != nullptr) nc->CommDestroy(x->comm);
     if (x->host_counts != nullptr) cudaFreeHost(x->host_counts);
+    if (x->have_events)
+        for (int i = 0; i < 6; ++i) cudaEventDestroy(x->ev[i]);
     delete x;
     return IMX_OK;
 }
@@ -667,7 +701,7 @@ int imx_ep_workspace_bytes(const imx_ep_ctx* x, int n_local, int schedule, size_
 }
 
 int imx_ep_forward(imx_ep_ctx* x, const imx_moe_weights* w, const void* xin, int n_local, void* y, void* workspace,
-                   size_t workspace_bytes, void* stream, int schedule, imx_ep_info* info) {
+                   size_t workspace_bytes, void* stream, int schedule, imx_ep_info* info, const imx_moe_trace* trace) {
     IMX_REQUIRE(x != nullptr && w != nullptr && w->router_w != nullptr, "ep_forward: context and weights are required");
     IMX_REQUIRE(n_local > 0 && xin != nullptr && y != nullptr, "ep_forward: every rank brings the same positive number of tokens");
     IMX_REQUIRE(((uintptr_t)xin % 16) == 0 && ((uintptr_t)y % 16) == 0, "ep_forward: x and y must be 16-byte aligned");
@@ -685,7 +719,7 @@ int imx_ep_forward(imx_ep_ctx* x, const imx_moe_weights* w, const void* xin, int
         return forward_gathered(*x, w, xin, n_local, y, workspace, workspace_bytes, (cudaStream_t)stream, info);
     }
     IMX_REQUIRE(s == IMX_EP_ALL_TO_ALL, "ep_forward: unknown schedule %d", schedule);
-    return forward_a2a(*x, w, xin, n_local, y, workspace, workspace_bytes, (cudaStream_t)stream, info);
+    return forward_a2a(*x, w, xin, n_local, y, workspace, workspace_bytes, (cudaStream_t)stream, info, trace);
 }
 
 }  // extern "C"

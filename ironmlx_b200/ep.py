@@ -395,7 +395,10 @@ class ExpertParallel:
             self._ws[key] = ws
         return ws
 
-    def forward(self, x: torch.Tensor, schedule: str = "auto", y: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, schedule: str = "auto", y: Optional[torch.Tensor] = None, timed: bool = False,
+                trace: bool = False):
+        """Collective.  timed: fill `info.phase_ms` (all-to-all schedule; synchronises).  trace: also return the
+        local tokens' routing and dispatch permutation (all-to-all schedule)."""
         if x.dtype != torch.bfloat16 or not x.is_cuda or x.shape[-1] != self.hidden:
             raise _lib.IronMLXError(_lib.ERR_INVALID, "ExpertParallel: x must be a bfloat16 CUDA tensor [n, hidden]")
         x = x.contiguous()
@@ -403,10 +406,21 @@ class ExpertParallel:
         ws = self.workspace(n, schedule, x.device)
         if y is None:
             y = torch.empty_like(x)
+        tr, tensors = None, None
+        if trace:
+            k, e = self.cfg.top_k, self.cfg.num_experts
+            i32 = dict(dtype=torch.int32, device=x.device)
+            tensors = {"topk_idx": torch.empty(n, k, **i32), "topk_w": torch.empty(n, k, device=x.device),
+                       "counts": torch.empty(e, **i32), "offsets": torch.empty(e + 1, **i32),
+                       "perm": torch.empty(n * k, **i32), "inv_perm": torch.empty(n * k, **i32),
+                       "shared_gate": torch.empty(n, device=x.device)}
+            tr = _lib.MoETrace(**{name: t.data_ptr() for name, t in tensors.items()})
+        self.info.want_timing = int(timed)
         check(lib().imx_ep_forward(self._ctx, C.byref(self._weights), x.data_ptr(), n, y.data_ptr(), ws.data_ptr(),
-                                   ws.numel(), ops.stream_ptr(), _lib.EP_SCHEDULE[schedule], C.byref(self.info)))
+                                   ws.numel(), ops.stream_ptr(), _lib.EP_SCHEDULE[schedule], C.byref(self.info),
+                                   None if tr is None else C.byref(tr)))
         self._last_ws = ws
-        return y
+        return (y, tensors) if trace else y
 
     def check_status(self) -> None:
         ws = getattr(self, "_last_ws", None)
@@ -428,11 +442,15 @@ def build_local(cfg, device, rank: int, world: int) -> LocalExperts:
     wl = Workload(cfg)
     e_loc = cfg.num_experts // world
     lo = rank * e_loc
-    gscale = None
+    gs_gu = gs_dn = None
     if cfg.mode == "nvfp4":
-        raise _lib.IronMLXError(_lib.ERR_INVALID, "nvfp4 tensor scales need the whole tensor: not wired for EP yet")
-    gate_up = synthetic._quantize_stack(lambda e: wl.expert_gate_up(lo + e), e_loc, cfg, device)
-    down = synthetic._quantize_stack(lambda e: wl.expert_down(lo + e), e_loc, cfg, device)
+        # one fp32 scale per stacked tensor, derived from ALL experts so that every rank quantizes its block exactly
+        # as the single-GPU block does
+        import numpy as np
+        gs_gu = synthetic.nvfp4_tensor_scale(max(float(np.abs(wl.expert_gate_up(e)).max()) for e in range(cfg.num_experts)))
+        gs_dn = synthetic.nvfp4_tensor_scale(max(float(np.abs(wl.expert_down(e)).max()) for e in range(cfg.num_experts)))
+    gate_up = synthetic._quantize_stack(lambda e: wl.expert_gate_up(lo + e), e_loc, cfg, device, gs_gu)
+    down = synthetic._quantize_stack(lambda e: wl.expert_down(lo + e), e_loc, cfg, device, gs_dn)
     out = LocalExperts(synthetic._bf16(wl.router_weight(), device), gate_up, down)
     if cfg.shared_intermediate:
         mlp = nn.MLP(*(synthetic._single(synthetic._quantize_stack(lambda e, nm=nm: wl.shared(nm), 1, cfg, device))

@@ -18,10 +18,10 @@ def nvfp4_tensor_scale(amax: float) -> float:
     return max(float(amax), 1e-30) / (6.0 * 448.0)
 
 
-def _quantize_stack(blocks_fn, count: int, cfg: MoEConfig, device) -> nn.QuantizedLinear:
+def _quantize_stack(blocks_fn, count: int, cfg: MoEConfig, device, gscale=None) -> nn.QuantizedLinear:
+    """gscale: nvfp4 tensor scale to quantize against (default: derived from these blocks)."""
     ws, ss, bs = [], [], []
-    gscale = None
-    if cfg.mode == "nvfp4":
+    if cfg.mode == "nvfp4" and gscale is None:
         gscale = nvfp4_tensor_scale(max(float(np.abs(blocks_fn(e)).max()) for e in range(count)))
     for e in range(count):
         w = torch.from_numpy(blocks_fn(e)).to(device)
@@ -40,23 +40,17 @@ def _single(q: nn.QuantizedLinear) -> nn.QuantizedLinear:
                               q.group_size, q.bits, q.mode, q.global_scale)
 
 
-def build_moe(cfg: MoEConfig, device="cuda", expert_range=None, path: str = "auto") -> nn.MoEMLP:
-    """expert_range=(lo, hi) keeps only those experts' weights (expert
-    parallelism); the router always covers all experts."""
+def build_moe(cfg: MoEConfig, device="cuda", path: str = "auto") -> nn.MoEMLP:
+    """The whole block of a configuration on one device (one rank's share of it: ironmlx_b200.ep.build_local)."""
     wl = Workload(cfg)
-    lo, hi = expert_range if expert_range is not None else (0, cfg.num_experts)
-    gate_up = _quantize_stack(lambda e: wl.expert_gate_up(lo + e), hi - lo, cfg, device)
-    down = _quantize_stack(lambda e: wl.expert_down(lo + e), hi - lo, cfg, device)
+    gate_up = _quantize_stack(lambda e: wl.expert_gate_up(e), cfg.num_experts, cfg, device)
+    down = _quantize_stack(lambda e: wl.expert_down(e), cfg.num_experts, cfg, device)
     shared = shared_gate = None
     if cfg.shared_intermediate:
         shared = nn.MLP(*(_single(_quantize_stack(lambda e, n=n: wl.shared(n), 1, cfg, device))
                           for n in ("gate_proj", "up_proj", "down_proj")))
         shared_gate = nn.Linear(_bf16(wl.shared_gate_weight(), device))
     bias = wl.router_logit_bias()
-    moe = nn.MoEMLP.__new__(nn.MoEMLP)
     router = nn.Linear(_bf16(wl.router_weight(), device))
-    if expert_range is None:
-        nn.MoEMLP.__init__(moe, router, nn.FusedExperts(gate_up, down), shared, shared_gate, cfg.top_k,
-                           cfg.norm_topk_prob, None if bias is None else torch.from_numpy(bias).to(device), path)
-        return moe
-    raise NotImplementedError("expert-parallel construction lives in ironmlx_b200.ep")
+    return nn.MoEMLP(router, nn.FusedExperts(gate_up, down), shared, shared_gate, cfg.top_k, cfg.norm_topk_prob,
+                     None if bias is None else torch.from_numpy(bias).to(device), path)
