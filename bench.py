@@ -439,13 +439,17 @@ def multi_gpu(args, dev, rank, world, barrier):
     lib = _lib.lib()
     _, tf_peak, which = peaks()
 
-    def build(cfg, n_local):
-        moe = ep.ExpertParallel(ep.build_local(cfg, dev, rank, world), cfg.num_experts, cfg.top_k, cfg.norm_topk_prob,
-                                cfg.hidden, cfg.intermediate, cfg.shared_intermediate)
-        return moe
+    def note(msg):                                   # progress on stderr: a collective that never returns shows where
+        if rank == 0:
+            print(f"[bench] {msg}", file=sys.stderr, flush=True)
+
+    def build(cfg, comm_of=None):
+        return ep.ExpertParallel(ep.build_local(cfg, dev, rank, world), cfg.num_experts, cfg.top_k, cfg.norm_topk_prob,
+                                 cfg.hidden, cfg.intermediate, cfg.shared_intermediate, comm_of=comm_of)
 
     # ---- headline: decode step, cfg.tokens tokens per rank, gathered schedule replayed as one CUDA graph ----
-    moe = build(cfg, cfg.tokens)
+    moe = build(cfg)
+    note("context and communicator up")
     x = torch.from_numpy(Workload(cfg).activations(block=rank)).to(dev).to(torch.bfloat16)
     xd, y = x.clone(), torch.empty_like(x)
     for _ in range(3):
@@ -469,6 +473,7 @@ def multi_gpu(args, dev, rank, world, barrier):
         moe.forward(xd, "gathered", y)
         launches = int(lib.imx_launch_count() - c0)
     step = (lambda: graph.replay()) if graph is not None else (lambda: moe.forward(xd, "gathered", y))
+    note(f"decode step recorded ({'graph' if graph is not None else 'plain launches'}, {launches} kernels)")
     ms, clocks = timed_steps(step, args.steps, args.warmup, barrier, dev, world, dev.index or 0)
     xh, yh = x.cpu().pin_memory(), torch.empty_like(x).cpu().pin_memory()
 
@@ -477,9 +482,11 @@ def multi_gpu(args, dev, rank, world, barrier):
         step()
         yh.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+    note(f"decode step timed: {ms:.4f} ms")
     e2e_ms = wall_steps(e2e_step, max(10, args.steps // 10), barrier, dev, world)
     torch.cuda.synchronize()
     moe.check_status()
+    note("end-to-end timed")
     y_timed = y.clone()
     info = {"schedule": int(moe.info.schedule), "bytes_sent": int(moe.info.bytes_sent)}
 
@@ -503,8 +510,10 @@ def multi_gpu(args, dev, rank, world, barrier):
                                             torch.equal(tr_a2a["topk_idx"], tr1["topk_idx"]))
             parity["all_to_all_rel_l2_vs_single_gpu"] = rel_l2(y_a2a.float().cpu().numpy(), y1.float().cpu().numpy())
         del full
-    moe.close()
-    del moe
+    # (the context and its communicator stay alive to the end: NCCL can block in its destructor while a captured
+    # graph still holds its collectives; the prefill block below borrows the same communicator)
+    first = moe
+    first.w = None                                   # this block's weights are no longer needed
     torch.cuda.empty_cache()
 
     tokens_per_step = cfg.tokens * world
@@ -530,11 +539,13 @@ def multi_gpu(args, dev, rank, world, barrier):
     if not args.no_prefill and args.config == "c2" and not (args.tokens or args.experts):
         pcfg = config_from(args, "c3")
         n_loc = pcfg.tokens // world
-        pmoe = build(pcfg, n_loc)
+        note("parity of the decode step checked; prefill block")
+        pmoe = build(pcfg, comm_of=first)
         px = torch.from_numpy(Workload(pcfg).activations()[rank * n_loc:(rank + 1) * n_loc]).to(dev).to(torch.bfloat16)
         py = torch.empty_like(px)
         psteps = args.prefill_steps or min(args.steps, 50)
         pms, pclocks = timed_steps(lambda: pmoe.forward(px, "a2a", py), psteps, args.warmup, barrier, dev, world, dev.index or 0)
+        note(f"prefill step timed: {pms:.4f} ms")
         phases = np.zeros(5)
         reps = 10
         for _ in range(reps):
@@ -569,7 +580,6 @@ def multi_gpu(args, dev, rank, world, barrier):
             "peak_source": f"of {which} (bf16 burst, x{world})", "clocks": pclocks, "parity": pparity,
             "exchange": "NCCL grouped ncclSend/ncclRecv of fp16 rows each way + an all-gather of the [E] counts (one host synchronisation)",
         }
-        pmoe.close()
     return line
 
 

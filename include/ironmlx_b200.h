@@ -302,6 +302,10 @@ IMX_API int imx_ep_unique_id(void* id128);
 IMX_API int imx_ep_create(const imx_moe_config* cfg, const void* unique_id, int rank, int world, imx_ep_ctx** ctx);
 /* The same on a communicator the host already has (an ncclComm_t); it is borrowed, not destroyed. */
 IMX_API int imx_ep_create_from_comm(const imx_moe_config* cfg, void* nccl_comm, int rank, int world, imx_ep_ctx** ctx);
+/* The context's ncclComm_t (to build further contexts on it with imx_ep_create_from_comm). */
+IMX_API void* imx_ep_comm(const imx_ep_ctx* ctx);
+/* Frees the context; a communicator the context created itself is destroyed with it: first release every
+ * captured CUDA graph that holds its collectives (NCCL can block in its destructor otherwise). */
 IMX_API int imx_ep_destroy(imx_ep_ctx* ctx);
 /* Scratch bytes for n_local tokens per rank (all-to-all: sized for every assignment of every rank landing here). */
 IMX_API int imx_ep_workspace_bytes(const imx_ep_ctx* ctx, int n_local, int schedule, size_t* bytes);

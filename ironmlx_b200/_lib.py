@@ -84,6 +84,7 @@ SIGNATURES = {
     "imx_ep_create": (_i, [C.POINTER(MoEConfig), _vp, _i, _i, C.POINTER(_vp)]),
     "imx_ep_create_from_comm": (_i, [C.POINTER(MoEConfig), _vp, _i, _i, C.POINTER(_vp)]),
     "imx_ep_destroy": (_i, [_vp]),
+    "imx_ep_comm": (_vp, [_vp]),
     "imx_ep_workspace_bytes": (_i, [_vp, _i, _i, C.POINTER(_sz)]),
     "imx_ep_forward": (_i, [_vp, C.POINTER(MoEWeights), _vp, _i, _vp, _vp, _sz, _vp, _i, C.POINTER(EpInfo),
                             C.POINTER(MoETrace)]),

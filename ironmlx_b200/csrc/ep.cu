@@ -681,6 +681,8 @@ int imx_ep_create_from_comm(const imx_moe_config* cfg, void* nccl_comm, int rank
     return IMX_OK;
 }
 
+void* imx_ep_comm(const imx_ep_ctx* x) { return x == nullptr ? nullptr : (void*)x->comm; }
+
 int imx_ep_destroy(imx_ep_ctx* x) {
     if (x == nullptr) return IMX_OK;
     const NcclApi* nc = nccl_api();

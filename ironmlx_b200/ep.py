@@ -348,7 +348,10 @@ class ExpertParallel:
     rank 0 through `torch.distributed` (any backend), which is otherwise not used on the data path."""
 
     def __init__(self, weights: LocalExperts, num_experts: int, top_k: int, norm_topk_prob: bool, hidden: int,
-                 intermediate: int, shared_intermediate: int, group=None, path: str = "auto"):
+                 intermediate: int, shared_intermediate: int, group=None, path: str = "auto",
+                 comm_of: Optional["ExpertParallel"] = None):
+        """comm_of: another instance of this process whose communicator is borrowed (one communicator per set
+        of ranks is enough; the instance that created it must outlive this one)."""
         self.w = weights
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -357,17 +360,22 @@ class ExpertParallel:
                              _lib.MODE[q.mode], q.bits, q.group_size, _lib.PATH[path])
         self.hidden = hidden
         dev = weights.router_w.device
-        uid = torch.zeros(128, dtype=torch.uint8)
-        if self.rank == 0:
-            buf = (C.c_ubyte * 128)()
-            check(lib().imx_ep_unique_id(buf))
-            uid = torch.tensor(list(buf), dtype=torch.uint8)
-        uid = uid.to(dev) if dist.get_backend(group) == "nccl" else uid
-        dist.broadcast(uid, 0, group=group)
-        raw = bytes(uid.cpu().tolist())
         self._ctx = C.c_void_p()
+        self._comm_owner = comm_of
         with torch.cuda.device(dev):
-            check(lib().imx_ep_create(C.byref(self.cfg), raw, self.rank, self.world, C.byref(self._ctx)))
+            if comm_of is not None:
+                check(lib().imx_ep_create_from_comm(C.byref(self.cfg), lib().imx_ep_comm(comm_of._ctx), self.rank,
+                                                    self.world, C.byref(self._ctx)))
+            else:
+                uid = torch.zeros(128, dtype=torch.uint8)
+                if self.rank == 0:
+                    buf = (C.c_ubyte * 128)()
+                    check(lib().imx_ep_unique_id(buf))
+                    uid = torch.tensor(list(buf), dtype=torch.uint8)
+                uid = uid.to(dev) if dist.get_backend(group) == "nccl" else uid
+                dist.broadcast(uid, 0, group=group)
+                raw = bytes(uid.cpu().tolist())
+                check(lib().imx_ep_create(C.byref(self.cfg), raw, self.rank, self.world, C.byref(self._ctx)))
         self._ws = {}
         self.info = _lib.EpInfo()
         self._weights = self._make_weights()
@@ -428,6 +436,7 @@ class ExpertParallel:
             check(lib().imx_moe_status(ws.data_ptr(), ops.stream_ptr()))
 
     def close(self) -> None:
+        """Frees the context (and the communicator it created).  Release CUDA graphs that captured `forward` first."""
         if self._ctx:
             lib().imx_ep_destroy(self._ctx)
             self._ctx = C.c_void_p()
