@@ -176,6 +176,12 @@ IMX_API int imx_moe_forward_host(const imx_moe_config* cfg, const imx_moe_weight
  * ran out: the call's output is incomplete). */
 IMX_API int imx_moe_status(void* workspace, void* stream);
 
+/* The expert kernels carry their intermediate rows in fp16 (SwiGLU outputs; on the tensor-core path also
+ * the expert rows) and clamp what exceeds its range (+-65504).  A clamp changes the result, so it is counted in
+ * the workspace (per value on the decode paths, per thread and tile on the tensor-core path): this reads the
+ * count accumulated since the last call, after synchronising the stream, and clears it.  0 = nothing clamped. */
+IMX_API int imx_moe_saturations(void* workspace, void* stream, long long* count);
+
 /* ── stages, for expert parallelism and stage-level parity ─────────────── */
 
 /* Router (moe.rs:67-82): logits = x.W_r^T (+bias), fp32 softmax, top-k in
@@ -331,6 +337,30 @@ IMX_API int imx_dequantize(const imx_qtensor* w, int rows, int in, int group_siz
 IMX_API int imx_quantized_matmul(const void* x, int m, const imx_qtensor* w, int n_out, int in,
                          int transpose, int group_size, int bits, int mode, void* y,
                          void* stream);
+
+/* The same product (transpose != 0 form) on the expert kernels: the second expert product is this
+ * contraction, so the call runs that kernel alone as a one-expert problem -- the tensor-map decode
+ * kernel for few rows, the tcgen05 kernel from 32 rows up -- and falls back to the kernel above for
+ * shapes neither takes.  `QuantizedLinear::forward_with_stream` (mlx/src/nn/linear.rs:51-63) with
+ * caller-provided scratch (zero-filled once, 256-byte aligned). */
+IMX_API int imx_quantized_matmul_scratch_bytes(int m, int n_out, int in, int group_size, int bits, int mode,
+                                       size_t* bytes);
+IMX_API int imx_quantized_matmul_ws(const void* x, int m, const imx_qtensor* w, int n_out, int in, int group_size,
+                            int bits, int mode, void* y, void* scratch, size_t scratch_bytes, void* stream);
+
+/* y[m, hidden] = down( silu(gate(x)) * up(x) ) for ONE expert over all m rows, bf16 in and out:
+ * `Expert::forward_with_stream` (mlx/src/nn/moe.rs:26-32) and `MLP::forward_with_stream`
+ * (mlx/src/nn/mlp.rs:27-33).  gate_up: [2*intermediate, hidden..] with the gate rows first (one expert of
+ * the fused checkpoint tensor, or gate_proj and up_proj stacked); down: [hidden, intermediate..].
+ * cfg: hidden, intermediate and the format are read. */
+IMX_API int imx_expert_scratch_bytes(const imx_moe_config* cfg, int m, size_t* bytes);
+IMX_API int imx_expert_forward(const imx_moe_config* cfg, const imx_qtensor* gate_up, const imx_qtensor* down,
+                       const void* x, int m, void* y, void* scratch, size_t scratch_bytes, void* stream);
+
+/* y[m, n_out] = x[m, in] @ w[n_out, in]^T (+ bias[n_out]), all bf16, fp32 accumulation:
+ * dense `Linear::forward_with_stream` (mlx/src/nn/linear.rs:170-177); bias may be NULL. */
+IMX_API int imx_linear(const void* x, int m, int in, const void* w, int n_out, const void* bias, void* y,
+               void* stream);
 
 /* Quantize w[rows, in] (fp32) into packed values, scales and biases
  * (absent from the reference's wrappers, which only consume checkpoints that

@@ -79,6 +79,38 @@ inline int mode_id(const std::string& mode) {
     throw Error(IMX_ERR_INVALID, "unknown quantization mode '" + mode + "'");
 }
 
+// Device scratch of the layer calls: grown on demand, zero-filled (its first word is a device status word),
+// one per host thread.
+class Scratch {
+public:
+    Scratch() = default;
+    Scratch(const Scratch&) = delete;
+    Scratch& operator=(const Scratch&) = delete;
+    ~Scratch() {
+        if (ptr_) cudaFree(ptr_);
+    }
+    void* get(size_t need) {
+        if (need > bytes_) {
+            if (ptr_) check_cuda(cudaFree(ptr_));
+            ptr_ = nullptr;
+            bytes_ = 0;
+            check_cuda(cudaMalloc(&ptr_, need));
+            check_cuda(cudaMemset(ptr_, 0, need));
+            bytes_ = need;
+        }
+        return ptr_;
+    }
+    size_t bytes() const { return bytes_; }
+    static Scratch& local() {
+        static thread_local Scratch s;
+        return s;
+    }
+
+private:
+    void* ptr_ = nullptr;
+    size_t bytes_ = 0;
+};
+
 namespace ops {
 
 // x [M, in] (bf16) times a packed weight [out, in] (transpose = true) or [in, out] (false).
@@ -87,7 +119,15 @@ inline void quantized_matmul(const Array& x, const Array& w, const Array& scales
                              float global_scale = 1.f) {
     imx_qtensor q{w.ptr, scales.ptr, biases ? biases->ptr : nullptr, global_scale};
     const int in = (int)x.dim(-1), m = (int)(x.size() / in), n_out = (int)y.dim(-1);
-    check(imx_quantized_matmul(x.ptr, m, &q, n_out, in, transpose ? 1 : 0, group_size, bits, mode_id(mode), y.ptr, stream));
+    if (transpose) {     // the layers' form: on the expert kernels where they take the shape
+        size_t need = 0;
+        check(imx_quantized_matmul_scratch_bytes(m, n_out, in, group_size, bits, mode_id(mode), &need));
+        Scratch& sc = Scratch::local();
+        void* ws = sc.get(need);
+        check(imx_quantized_matmul_ws(x.ptr, m, &q, n_out, in, group_size, bits, mode_id(mode), y.ptr, ws, sc.bytes(), stream));
+        return;
+    }
+    check(imx_quantized_matmul(x.ptr, m, &q, n_out, in, 0, group_size, bits, mode_id(mode), y.ptr, stream));
 }
 
 // Packed weight [rows, in] -> dense bf16 / fp32 `out`.
@@ -101,10 +141,17 @@ inline void dequantize(const Array& w, const Array& scales, const Array* biases,
 
 }  // namespace ops
 
-// Dense bf16 projection; inside the block it is only a holder of its weight (router, shared-expert gate).
+// Dense bf16 projection x . W^T (+ b) (mlx/src/nn/linear.rs:129-177); inside the block it is only a holder of
+// its weight (router, shared-expert gate).
 struct Linear {
-    Array weight;   // [out, in] bf16
-    explicit Linear(Array w = {}) : weight(std::move(w)) {}
+    Array weight;                 // [out, in] bf16
+    std::optional<Array> bias;    // [out] bf16
+    explicit Linear(Array w = {}, std::optional<Array> b = std::nullopt) : weight(std::move(w)), bias(std::move(b)) {}
+    void forward_with_stream(const Array& x, Array& y, cudaStream_t stream = nullptr) const {
+        const int in = (int)weight.dim(1), n_out = (int)weight.dim(0);
+        if (x.dim(-1) != in || y.dim(-1) != n_out) throw Error(IMX_ERR_INVALID, "Linear: shapes do not match the weight");
+        check(imx_linear(x.ptr, (int)(x.size() / in), in, weight.ptr, n_out, bias ? bias->ptr : nullptr, y.ptr, stream));
+    }
 };
 
 struct QuantizedLinear {
@@ -155,10 +202,75 @@ struct RMSNorm {
     }
 };
 
-// SwiGLU MLP: down(silu(gate(x)) * up(x)); the shared expert of the block.
+// SwiGLU MLP: down(silu(gate(x)) * up(x)) (mlx/src/nn/mlp.rs:12-33); the shared expert of the block.  Also one
+// routed expert (`Expert`, mlx/src/nn/moe.rs:11-33): its projections are then views into the fused tensors.
+// forward_with_stream needs the gate and up rows as ONE [2I, .] tensor: adjacent views are used in place, separate
+// tensors are stacked once into device memory the object owns.
 struct MLP {
     QuantizedLinear gate_proj, up_proj, down_proj;
+
+    MLP() = default;
+    MLP(QuantizedLinear g, QuantizedLinear u, QuantizedLinear d)
+        : gate_proj(std::move(g)), up_proj(std::move(u)), down_proj(std::move(d)) {}
+    MLP(const MLP& o) : gate_proj(o.gate_proj), up_proj(o.up_proj), down_proj(o.down_proj) {}
+    MLP& operator=(const MLP& o) {
+        if (this != &o) {
+            release();
+            gate_proj = o.gate_proj;
+            up_proj = o.up_proj;
+            down_proj = o.down_proj;
+        }
+        return *this;
+    }
+    ~MLP() { release(); }
+
+    void forward_with_stream(const Array& x, Array& y, cudaStream_t stream = nullptr) {
+        const int hidden = (int)x.dim(-1), m = (int)(x.size() / hidden);
+        imx_moe_config c{};
+        c.hidden = hidden;
+        c.num_experts = 1;
+        c.top_k = 1;
+        c.intermediate = (int)gate_proj.weight.dim(0);
+        c.norm_topk_prob = 1;
+        c.mode = mode_id(gate_proj.mode);
+        c.bits = gate_proj.bits;
+        c.group_size = gate_proj.group_size;
+        const imx_qtensor gu = fused_gate_up(stream), dn = down_proj.qtensor();
+        size_t need = 0;
+        check(imx_expert_scratch_bytes(&c, m, &need));
+        Scratch& sc = Scratch::local();
+        void* ws = sc.get(need);
+        check(imx_expert_forward(&c, &gu, &dn, x.ptr, m, y.ptr, ws, sc.bytes(), stream));
+    }
+
+private:
+    static bool adjacent(const Array& a, const Array& b) { return (const char*)b.ptr == (const char*)a.ptr + a.nbytes(); }
+    imx_qtensor fused_gate_up(cudaStream_t stream) {
+        const bool has_b = gate_proj.biases.has_value();
+        if (adjacent(gate_proj.weight, up_proj.weight) && adjacent(gate_proj.scales, up_proj.scales) &&
+            (!has_b || adjacent(*gate_proj.biases, *up_proj.biases)))
+            return gate_proj.qtensor();
+        if (!own_[0]) {
+            auto stack = [&](const Array& a, const Array& b, void** out) {
+                check_cuda(cudaMalloc(out, a.nbytes() + b.nbytes()));
+                check_cuda(cudaMemcpyAsync(*out, a.ptr, a.nbytes(), cudaMemcpyDeviceToDevice, stream));
+                check_cuda(cudaMemcpyAsync((char*)*out + a.nbytes(), b.ptr, b.nbytes(), cudaMemcpyDeviceToDevice, stream));
+            };
+            stack(gate_proj.weight, up_proj.weight, &own_[0]);
+            stack(gate_proj.scales, up_proj.scales, &own_[1]);
+            if (has_b) stack(*gate_proj.biases, *up_proj.biases, &own_[2]);
+        }
+        return imx_qtensor{own_[0], own_[1], own_[2], gate_proj.global_scale};
+    }
+    void release() {
+        for (void*& p : own_) {
+            if (p) cudaFree(p);
+            p = nullptr;
+        }
+    }
+    void* own_[3] = {nullptr, nullptr, nullptr};
 };
+using Expert = MLP;
 
 // All routed experts as the two fused checkpoint tensors: gate_up [E, 2I, .] (gate rows first), down [E, H, .].
 struct FusedExperts {

@@ -67,6 +67,8 @@ SIGNATURES = {
                                    C.POINTER(C.c_float)]),
     "imx_moe_forward_host": (_i, [C.POINTER(MoEConfig), C.POINTER(MoEWeights), _vp, _i, _vp, _vp, _sz, _vp]),
     "imx_moe_status": (_i, [_vp, _vp]),
+    "imx_testing_decode_handoff": (None, [_i, _i]),
+    "imx_moe_saturations": (_i, [_vp, _vp, C.POINTER(C.c_longlong)]),
     "imx_moe_route": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "imx_moe_route_scratch_bytes": (_i, [_i, _i, _i, C.POINTER(_sz)]),
     "imx_moe_route_ws": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
@@ -90,6 +92,11 @@ SIGNATURES = {
                             C.POINTER(MoETrace)]),
     "imx_dequantize": (_i, [C.POINTER(QTensor), _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "imx_quantized_matmul": (_i, [_vp, _i, C.POINTER(QTensor), _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "imx_quantized_matmul_scratch_bytes": (_i, [_i, _i, _i, _i, _i, _i, C.POINTER(_sz)]),
+    "imx_quantized_matmul_ws": (_i, [_vp, _i, C.POINTER(QTensor), _i, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
+    "imx_expert_scratch_bytes": (_i, [C.POINTER(MoEConfig), _i, C.POINTER(_sz)]),
+    "imx_expert_forward": (_i, [C.POINTER(MoEConfig), C.POINTER(QTensor), C.POINTER(QTensor), _vp, _i, _vp, _vp, _sz, _vp]),
+    "imx_linear": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp]),
     "imx_quantize": (_i, [_vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp]),
     "imx_gather_qmm": (_i, [_vp, _vp, C.POINTER(QTensor), _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]),
 }

@@ -502,6 +502,20 @@ int imx_moe_status(void* workspace, void* stream_) {
     return IMX_OK;
 }
 
+void imx_testing_decode_handoff(int spin_limit, int withhold) { testing_decode_handoff(spin_limit, withhold); }
+
+int imx_moe_saturations(void* workspace, void* stream_, long long* count) {
+    IMX_REQUIRE(workspace != nullptr && count != nullptr, "saturations: workspace and count are required");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int32_t v = 0;
+    int32_t* word = reinterpret_cast<int32_t*>(workspace) + kStatusSaturations;
+    IMX_CHECK_CUDA(cudaMemcpyAsync(&v, word, sizeof(v), cudaMemcpyDeviceToHost, stream));
+    IMX_CHECK_CUDA(cudaStreamSynchronize(stream));
+    if (v != 0) IMX_CHECK_CUDA(cudaMemsetAsync(word, 0, sizeof(v), stream));
+    *count = v;
+    return IMX_OK;
+}
+
 int imx_moe_route(const void* x, int n_tokens, int hidden, const void* router_w, const float* logit_bias,
                   int num_experts, int top_k, int norm_topk_prob, const void* shared_gate_w,
                   int32_t* topk_idx, float* topk_w, float* shared_gate, void* x_f16, void* stream) {

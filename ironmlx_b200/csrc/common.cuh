@@ -114,6 +114,13 @@ __device__ __forceinline__ __half f32_to_f16_sat(float v) {
     v = fminf(fmaxf(v, -65504.0f), 65504.0f);
     return __float2half_rn(v);
 }
+// The same, counting the values that had to be clamped (word 4 of a workspace's status block, read and cleared
+// by imx_moe_saturations): a clamp changes the result and must not pass unnoticed.
+constexpr int kStatusSaturations = 4;
+__device__ __forceinline__ __half f32_to_f16_sat(float v, int32_t* status) {
+    if (status != nullptr && fabsf(v) > 65504.0f) atomicAdd(status + kStatusSaturations, 1);
+    return f32_to_f16_sat(v);
+}
 #endif
 
 }  // namespace imx

@@ -196,7 +196,7 @@ __device__ __forceinline__ void epilogue(const GroupedArgs& a, const TaskCtx& c,
                     const float v = silu_f(acc[0][i] * c.gs[0]) * (acc[1][i] * c.gs[1]);
                     // stored in the permuted order the second product reads
                     const int col = (row & ~15) + permuted_pos<BITS>(row & 15);
-                    a.act[(size_t)(c.slot0 + slot_l) * a.act_stride + col] = f32_to_f16_sat(v);
+                    a.act[(size_t)(c.slot0 + slot_l) * a.act_stride + col] = f32_to_f16_sat(v, a.status);
                 }
             }
         } else {

@@ -266,7 +266,7 @@ __device__ __forceinline__ void finish(const GroupedArgs& a, const FpTask& c, fl
                 const int slot_l = 2 * t + (i & 1);
                 const int row = c.row0[0] + g + 8 * (i >> 1);
                 if (slot_l < c.rows)
-                    a.act[(size_t)(c.slot0 + slot_l) * a.act_stride + row] = f32_to_f16_sat(silu_f(r[0][i]) * r[1][i]);
+                    a.act[(size_t)(c.slot0 + slot_l) * a.act_stride + row] = f32_to_f16_sat(silu_f(r[0][i]) * r[1][i], a.status);
             }
         } else {
 #pragma unroll
@@ -366,8 +366,10 @@ int launch_mode(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid) {
     IMX_CHECK_CUDA(cudaGetDevice(&dev));
     IMX_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int mid_max = s.has_extra && s.x_mid > s.n_mid ? s.x_mid : s.n_mid;
-    decode_fp_kernel<MX, true><<<sms, kThreads, 0, stream>>>(a, mid_max / 16); IMX_LAUNCHED();
-    IMX_CHECK_CUDA(cudaGetLastError());
+    if (!a.second_only) {
+        decode_fp_kernel<MX, true><<<sms, kThreads, 0, stream>>>(a, mid_max / 16); IMX_LAUNCHED();
+        IMX_CHECK_CUDA(cudaGetLastError());
+    }
     if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
     decode_fp_kernel<MX, false><<<sms, kThreads, 0, stream>>>(a, s.n_in / 32); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());

@@ -200,8 +200,10 @@ int launch_bits(const GroupedArgs& a, int g128, cudaStream_t stream, cudaEvent_t
     IMX_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int mid_max = s.has_extra && s.x_mid > s.n_mid ? s.x_mid : s.n_mid;
     const int grid = sms;                       // one resident CTA of 8 warps per SM
-    decode_mma_kernel<BITS, true><<<grid, kThreads, 0, stream>>>(a, mid_max / 16, g128); IMX_LAUNCHED();
-    IMX_CHECK_CUDA(cudaGetLastError());
+    if (!a.second_only) {
+        decode_mma_kernel<BITS, true><<<grid, kThreads, 0, stream>>>(a, mid_max / 16, g128); IMX_LAUNCHED();
+        IMX_CHECK_CUDA(cudaGetLastError());
+    }
     if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
     decode_mma_kernel<BITS, false><<<grid, kThreads, 0, stream>>>(a, s.n_in / 32, g128); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());

@@ -33,6 +33,9 @@
 // fp32 partial sums over through the workspace.  Every wait is bounded.
 #include <cuda.h>
 
+#include <atomic>
+#include <cstring>
+
 #include "decode_common.cuh"
 
 namespace imx {
@@ -54,6 +57,8 @@ constexpr size_t smem_bytes(int warps, int stages, int sum_groups) {
 constexpr int kSpinLimit = 1 << 20;
 constexpr int kFlagSpinLimit = 1 << 22;
 constexpr float kUnscale = 16777216.f;         // 2^24: the accumulators are in units of 2^-24
+std::atomic<int> g_flag_spin_limit{kFlagSpinLimit};
+std::atomic<int> g_withhold_flags{0};
 
 // [0] the routed experts' stacked matrix, [1]/[2] the extra expert's matrix for tile 0 / tile 1 of a pair
 struct DecodeMaps {
@@ -158,7 +163,8 @@ __global__ void group_sums_kernel(const __half* __restrict__ in, const int32_t* 
 template <bool SWIGLU, int kWarps, int kStages>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const int st_r, const int st_x,
-                   const int flag_base, const int sum_groups, const __grid_constant__ DecodeMaps maps) {
+                   const int flag_base, const int sum_groups, const int flag_spin_limit, const int withhold_flags,
+                   const __grid_constant__ DecodeMaps maps) {
     constexpr int kSmemW = kWarps * kStages * kWBytes, kSmemS = kWarps * kStages * kSBytes;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -356,7 +362,7 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
                 for (int i = 0; i < 4; ++i) my_slot[(T * 4 + i) * 32 + lane] = acc[T][i];
             __threadfence();
             __syncwarp();
-            if (lane == 0) *reinterpret_cast<volatile int32_t*>(flags + gw) = 1;
+            if (lane == 0 && !withhold_flags) *reinterpret_cast<volatile int32_t*>(flags + gw) = 1;
         } else {
             if (cc.st + 1 < st_n) {
                 // owner of a pair that was cut: add the partials of the following warps, in warp order
@@ -368,7 +374,7 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
                     if (lane == 0) {
                         int spin = 0;
                         while (*reinterpret_cast<volatile int32_t*>(flags + w) == 0) {
-                            if (++spin > kFlagSpinLimit) {
+                            if (++spin > flag_spin_limit) {
                                 ok = 0;
                                 break;
                             }
@@ -400,7 +406,7 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
                         float v = silu_f(acc[0][i] * kUnscale) * (acc[1][i] * kUnscale);
                         if (row & 1) v *= 0.0625f;                                 // meets a [4,8) code in the second product
                         const int col = (row & ~15) + permuted_pos<4>(row & 15);   // the order the second product reads
-                        a.act[(size_t)(c_slot0 + slot_l) * a.act_stride + col] = f32_to_f16_sat(v);
+                        a.act[(size_t)(c_slot0 + slot_l) * a.act_stride + col] = f32_to_f16_sat(v, a.status);
                     }
                 }
             } else {
@@ -540,6 +546,14 @@ decode_tmap_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const 
 
 }  // namespace
 
+// Test hook (include/ironmlx_b200_testing.h): a short limit on the hand-off wait and flags that are never
+// raised make the wait run out, so that the path from an expired wait to the status word can be exercised
+// without hanging or faulting anything.
+void testing_decode_handoff(int spin_limit, int withhold) {
+    g_flag_spin_limit.store(spin_limit > 0 ? spin_limit : kFlagSpinLimit);
+    g_withhold_flags.store(withhold ? 1 : 0);
+}
+
 bool decode_tmap_supported(const ExpertSet& s) {
     const QFormat& f = s.fmt;
     if (f.mode != IMX_MODE_AFFINE || f.bits != 4 || f.group != 64) return false;
@@ -579,19 +593,23 @@ int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn
     // shared memory: the rings, plus (second product) a table of group sums as wide as the rows need, so that
     // what is not used stays with the L1 cache
     const size_t smem_gu = smem_bytes(kWarps, kStages, 0), smem_dn = smem_bytes(kWarps, kStages, g_mid);
-    if (!a.gsum_x_ready) {
-        const int n = a.n_in_rows * g_in;
-        group_sums_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a.in, nullptr, a.n_in_rows, g_in, s.n_in, a.gsum_x,
-                                                             a.n_rows_dev); IMX_LAUNCHED();
+    if (!a.second_only) {
+        if (!a.gsum_x_ready) {
+            const int n = a.n_in_rows * g_in;
+            group_sums_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a.in, nullptr, a.n_in_rows, g_in, s.n_in, a.gsum_x,
+                                                                 a.n_rows_dev); IMX_LAUNCHED();
+            IMX_CHECK_CUDA(cudaGetLastError());
+        }
+        decode_tmap_kernel<true, kWarps, kStages><<<grid, kWarps * 32, smem_gu, stream>>>(
+            a, s.n_mid / 16, x_mid / 16, s.n_in / kStageCodes, s.n_in / kStageCodes, 8, g_in, g_flag_spin_limit.load(),
+            g_withhold_flags.load(), gu); IMX_LAUNCHED();
         IMX_CHECK_CUDA(cudaGetLastError());
     }
-    decode_tmap_kernel<true, kWarps, kStages><<<grid, kWarps * 32, smem_gu, stream>>>(
-        a, s.n_mid / 16, x_mid / 16, s.n_in / kStageCodes, s.n_in / kStageCodes, 8, g_in, gu); IMX_LAUNCHED();
-    IMX_CHECK_CUDA(cudaGetLastError());
     if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
     // second product: every warp sums the groups of its unit's SwiGLU rows itself
     decode_tmap_kernel<false, kWarps, kStages><<<grid, kWarps * 32, smem_dn, stream>>>(
-        a, s.n_in / 32, s.n_in / 32, s.n_mid / kStageCodes, x_mid / kStageCodes, 8 + kFlagWarps, g_mid, dn); IMX_LAUNCHED();
+        a, s.n_in / 32, s.n_in / 32, s.n_mid / kStageCodes, x_mid / kStageCodes, 8 + kFlagWarps, g_mid, g_flag_spin_limit.load(),
+        g_withhold_flags.load(), dn); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }
@@ -600,19 +618,22 @@ int launch_with(const GroupedArgs& a, const DecodeMaps& gu, const DecodeMaps& dn
 
 int launch_decode_tmap(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid) {
     IMX_REQUIRE(decode_tmap_supported(a.set), "decode (tensor-map) path: format/shape not supported");
-    IMX_REQUIRE(a.partials != nullptr && a.sched != nullptr && a.gsum_x != nullptr && a.n_slots > 0 &&
-                    a.n_in_rows > 0,
+    IMX_REQUIRE(a.partials != nullptr && a.sched != nullptr && (a.gsum_x != nullptr || a.second_only) && a.n_slots > 0 &&
+                    (a.n_in_rows > 0 || a.second_only),
                 "decode (tensor-map) path: workspace buffers missing");
     if (a.max_units == 0) return IMX_OK;
     const ExpertSet& s = a.set;
     DeviceInfo di;
     IMX_TRY(current_device(&di));
     DecodeMaps gu, dn;
-    IMX_TRY(make_maps(s.gate, (size_t)s.num_experts * 2 * s.n_mid, s.n_in, &gu.w[0], &gu.s[0], &gu.b[0]));
+    if (!a.second_only) IMX_TRY(make_maps(s.gate, (size_t)s.num_experts * 2 * s.n_mid, s.n_in, &gu.w[0], &gu.s[0], &gu.b[0]));
+    else std::memset(&gu, 0, sizeof(gu));
     IMX_TRY(make_maps(s.down, (size_t)s.num_experts * s.n_in, s.n_mid, &dn.w[0], &dn.s[0], &dn.b[0]));
     if (s.has_extra) {
-        IMX_TRY(make_maps(s.x_gate, (size_t)s.x_mid, s.n_in, &gu.w[1], &gu.s[1], &gu.b[1]));
-        IMX_TRY(make_maps(s.x_up, (size_t)s.x_mid, s.n_in, &gu.w[2], &gu.s[2], &gu.b[2]));
+        if (!a.second_only) {
+            IMX_TRY(make_maps(s.x_gate, (size_t)s.x_mid, s.n_in, &gu.w[1], &gu.s[1], &gu.b[1]));
+            IMX_TRY(make_maps(s.x_up, (size_t)s.x_mid, s.n_in, &gu.w[2], &gu.s[2], &gu.b[2]));
+        }
         IMX_TRY(make_maps(s.x_down, (size_t)s.n_in, s.x_mid, &dn.w[1], &dn.s[1], &dn.b[1]));
     } else {
         gu.w[1] = gu.w[2] = gu.w[0]; gu.s[1] = gu.s[2] = gu.s[0]; gu.b[1] = gu.b[2] = gu.b[0];

@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(kGThreads) generic_grouped_kernel(GroupedArgs 
                 if (r >= u.rows) break;
                 const int slot = u.slot0 + r;
                 if (SWIGLU) {
-                    a.act[(size_t)slot * a.act_stride + row] = f32_to_f16_sat(silu_f(acc_a[r]) * acc_b[r]);
+                    a.act[(size_t)slot * a.act_stride + row] = f32_to_f16_sat(silu_f(acc_a[r]) * acc_b[r], a.status);
                 } else {
                     const float sc = a.row_scale ? a.row_scale[slot] : 1.f;
                     a.out[(size_t)slot * a.set.n_in + row] = acc_a[r] * sc;

@@ -121,6 +121,7 @@ struct GroupedArgs {
     __half* out16;                 // prefill path only: the same rows as fp16 instead (out is then unused), or nullptr
     const int32_t* out_index;      // prefill path only: output row of each slot (nullptr: the slot itself)
     int32_t* status;               // device status word
+    int second_only;               // run the second product alone: out = act . down^T (a plain quantized matmul)
 };
 
 bool decode_mma_supported(const ExpertSet& s);
@@ -129,6 +130,7 @@ int launch_decode_mma(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid
 // Tensor-map fed decode kernel (affine 4-bit, group 64); the preferred decode kernel where it applies.
 bool decode_tmap_supported(const ExpertSet& s);
 int launch_decode_tmap(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);
+void testing_decode_handoff(int spin_limit, int withhold);
 // Decode kernel of the block-scaled float formats (mxfp8, nvfp4).
 bool decode_fp_supported(const ExpertSet& s);
 int launch_decode_fp(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr);

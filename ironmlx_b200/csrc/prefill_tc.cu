@@ -46,6 +46,7 @@
 // is applied per row in the epilogue.
 #include <cuda.h>
 
+#include <cstring>
 #include <type_traits>
 
 #include "decode_common.cuh"
@@ -699,6 +700,7 @@ prefill_tc_kernel(const GroupedArgs a, const TcParams p, const __grid_constant__
             PROF_END(0)
             tc_fence_after();
             PROF_BEGIN
+            float peak = 0.f;                                       // largest magnitude this thread rounds to fp16 in the tile
             const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * DCOLS);
             auto release = [&]() {                                  // all of this warp's TMEM reads are done
                 tc_fence_before();
@@ -723,7 +725,9 @@ prefill_tc_kernel(const GroupedArgs a, const TcParams p, const __grid_constant__
                             float g0 = __uint_as_float(v[4 * j]), g1 = __uint_as_float(v[4 * j + 1]);
                             float u0 = __uint_as_float(v[4 * j + 2]), u1 = __uint_as_float(v[4 * j + 3]);
                             if (!AFFINE) { g0 *= rf[2 * gs]; g1 *= rf[2 * gs]; u0 *= rf[2 * gs + 1]; u1 *= rf[2 * gs + 1]; }
-                            o[j] = pack_f16_sat(silu_fast(g0) * u0, silu_fast(g1) * u1);
+                            const float r0 = silu_fast(g0) * u0, r1 = silu_fast(g1) * u1;
+                            peak = fmaxf(peak, fmaxf(fabsf(r0), fabsf(r1)));
+                            o[j] = pack_f16_sat(r0, r1);
                         }
                         const int col = t.ntile * 64 + (2 * q + gs) * 8 + (lane >> 2);
                         const int pos = (col & ~15) + (int)((p.pos_lut >> (4 * (col & 15))) & 0xf);
@@ -768,6 +772,7 @@ prefill_tc_kernel(const GroupedArgs a, const TcParams p, const __grid_constant__
                         const int orow = my < t.rows ? a.out_index[t.slot0 + my] : 0;
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
+                            peak = fmaxf(peak, fmaxf(fabsf(o[i]), fabsf(o[i + 1])));
                             const uint32_t h = pack_f16_sat(o[i], o[i + 1]);
                             const int r0 = __shfl_sync(0xffffffffu, orow, i), r1 = __shfl_sync(0xffffffffu, orow, i + 1);
                             if (i < n_ok) st_global_u16(a.out16 + (size_t)r0 * a.set.n_in + col, h);
@@ -776,6 +781,7 @@ prefill_tc_kernel(const GroupedArgs a, const TcParams p, const __grid_constant__
                     } else if (a.out16 != nullptr) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
+                            peak = fmaxf(peak, fmaxf(fabsf(o[i]), fabsf(o[i + 1])));
                             const uint32_t h = pack_f16_sat(o[i], o[i + 1]);
                             if (i < n_ok) st_global_u16(a.out16 + o0 + (size_t)i * a.set.n_in, h);
                             if (i + 1 < n_ok) st_global_u16(a.out16 + o0 + (size_t)(i + 1) * a.set.n_in, h >> 16);
@@ -787,6 +793,8 @@ prefill_tc_kernel(const GroupedArgs a, const TcParams p, const __grid_constant__
                     }
                 }
             }
+            // values beyond the fp16 range were clamped: counted (per thread and tile), never silent
+            if (peak > 65504.f && a.status != nullptr) atomicAdd(a.status + kStatusSaturations, 1);
             PROF_END(1)
             return true;
         });
@@ -948,11 +956,13 @@ struct Plan {
 template <int FMT>
 int launch_fmt(const GroupedArgs& a, const Plan& gu, const Plan& dn, bool ts, const TcMaps& mgu, const TcMaps& mdn, int sms,
                cudaStream_t stream, cudaEvent_t mid) {
-    if (!ts) prefill_tc_kernel<true, FMT, false, false, false><<<sms, kThreadsTc, gu.smem, stream>>>(a, gu.p, mgu);
-    else if (gu.wide) prefill_tc_kernel<true, FMT, true, true, false><<<sms, kThreadsTc, gu.smem, stream>>>(a, gu.p, mgu);
-    else prefill_tc_kernel<true, FMT, true, false, false><<<sms, kThreadsTc, gu.smem, stream>>>(a, gu.p, mgu);
-    IMX_LAUNCHED();
-    IMX_CHECK_CUDA(cudaGetLastError());
+    if (!a.second_only) {
+        if (!ts) prefill_tc_kernel<true, FMT, false, false, false><<<sms, kThreadsTc, gu.smem, stream>>>(a, gu.p, mgu);
+        else if (gu.wide) prefill_tc_kernel<true, FMT, true, true, false><<<sms, kThreadsTc, gu.smem, stream>>>(a, gu.p, mgu);
+        else prefill_tc_kernel<true, FMT, true, false, false><<<sms, kThreadsTc, gu.smem, stream>>>(a, gu.p, mgu);
+        IMX_LAUNCHED();
+        IMX_CHECK_CUDA(cudaGetLastError());
+    }
     if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
     if (!ts) prefill_tc_kernel<false, FMT, false, false, false><<<sms, kThreadsTc, dn.smem, stream>>>(a, dn.p, mdn);
     else if (dn.xr) prefill_tc_kernel<false, FMT, true, false, true><<<sms, kThreadsTc, dn.smem, stream>>>(a, dn.p, mdn);
@@ -986,7 +996,7 @@ bool prefill_tc_supported(const ExpertSet& s) {
 // activations everywhere, 2 = as 1 with the dequantized tile in shared memory (1, 2: cross-checks).
 int launch_prefill_tc(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid, int variant) {
     IMX_REQUIRE(prefill_tc_supported(a.set), "prefill path: format/shape not supported");
-    IMX_REQUIRE((a.row_index == nullptr || a.xs != nullptr) && a.n_slots > 0,
+    IMX_REQUIRE((a.row_index == nullptr || a.xs != nullptr || a.second_only) && a.n_slots > 0,
                 "prefill path: slot-ordered activation buffer missing");
     if (a.max_units == 0) return IMX_OK;
     const ExpertSet& s = a.set;
@@ -1034,8 +1044,8 @@ int launch_prefill_tc(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid
         out->xr = xr;
         return true;
     };
-    Plan gu, dn;
-    if (!(variant == 0 && plan(s.n_in, s.n_in, true, false, &gu)))
+    Plan gu = {}, dn = {};
+    if (!a.second_only && !(variant == 0 && plan(s.n_in, s.n_in, true, false, &gu)))
         IMX_REQUIRE(plan(s.n_in, s.n_in, false, false, &gu), "prefill path: sizes exceed shared memory");
     if (!(variant == 0 && plan(mid_max, mid_min, false, true, &dn)))
         IMX_REQUIRE(plan(mid_max, mid_min, false, false, &dn), "prefill path: sizes exceed shared memory");
@@ -1052,21 +1062,25 @@ int launch_prefill_tc(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid
 
     // activations in sorted-slot order (the `take_axis` of moe.rs:124-127, once for all experts)
     const __half* xsrc = a.in;                     // already slot-ordered when there is no row index
-    if (a.row_index != nullptr) {
+    if (a.row_index != nullptr && !a.second_only) {
         IMX_TRY(launch_gather_rows(a.in, a.row_index, a.n_slots, (size_t)s.n_in * 2, a.xs, stream));
         xsrc = a.xs;
     }
     TcMaps mgu, mdn;
+    std::memset(&mgu, 0, sizeof(mgu));
+    if (!a.second_only)
     IMX_TRY(make_tensor_map_2d(xsrc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.n_slots, (size_t)s.n_in, (size_t)s.n_in * 2, kTileK,
                                128, true, &mgu.x));
     IMX_TRY(make_tensor_map_2d(a.act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.n_slots, (size_t)mid_max, (size_t)a.act_stride * 2,
                                kTileK, 128, true, &mdn.x));
     // routed experts: gate and up rows live in one stacked matrix [E*2I, H]; down in [E*H, I]
-    IMX_TRY(make_q_maps(s.gate, (size_t)s.num_experts * 2 * s.n_mid, s.n_in, f, fmt, &mgu.w[0], &mgu.s[0], &mgu.b[0]));
+    if (!a.second_only) IMX_TRY(make_q_maps(s.gate, (size_t)s.num_experts * 2 * s.n_mid, s.n_in, f, fmt, &mgu.w[0], &mgu.s[0], &mgu.b[0]));
     IMX_TRY(make_q_maps(s.down, (size_t)s.num_experts * s.n_in, s.n_mid, f, fmt, &mdn.w[0], &mdn.s[0], &mdn.b[0]));
     if (s.has_extra) {
-        IMX_TRY(make_q_maps(s.x_gate, (size_t)s.x_mid, s.n_in, f, fmt, &mgu.w[1], &mgu.s[1], &mgu.b[1]));
-        IMX_TRY(make_q_maps(s.x_up, (size_t)s.x_mid, s.n_in, f, fmt, &mgu.w[2], &mgu.s[2], &mgu.b[2]));
+        if (!a.second_only) {
+            IMX_TRY(make_q_maps(s.x_gate, (size_t)s.x_mid, s.n_in, f, fmt, &mgu.w[1], &mgu.s[1], &mgu.b[1]));
+            IMX_TRY(make_q_maps(s.x_up, (size_t)s.x_mid, s.n_in, f, fmt, &mgu.w[2], &mgu.s[2], &mgu.b[2]));
+        }
         IMX_TRY(make_q_maps(s.x_down, (size_t)s.n_in, s.x_mid, f, fmt, &mdn.w[1], &mdn.s[1], &mdn.b[1]));
     } else {
         mgu.w[1] = mgu.w[2] = mgu.w[0]; mgu.s[1] = mgu.s[2] = mgu.s[0]; mgu.b[1] = mgu.b[2] = mgu.b[0];

@@ -26,13 +26,12 @@ from ._lib import IronMLXError, MoEConfig, MoETrace, MoEWeights, QTensor, check,
 class Linear:
     """Dense `x @ W^T (+ b)` (mlx/src/nn/linear.rs:129-177).  On the MoE path
     only the router and the shared-expert gate are dense, and both are consumed
-    inside the fused block, so this class only carries the weights."""
+    inside the fused block; called on its own it is one bf16 tensor-core GEMM."""
     weight: torch.Tensor
     bias: Optional[torch.Tensor] = None
 
     def forward_with_stream(self, x: torch.Tensor, stream=None) -> torch.Tensor:
-        raise IronMLXError(_lib.ERR_INVALID,
-                           "dense Linear is not part of the accelerated path; it is evaluated inside MoEMLP")
+        return ops.linear(x, self.weight, self.bias, stream)
 
 
 @dataclass
@@ -81,8 +80,33 @@ class QuantizedLinear:
 LinearLayer = Union[Linear, QuantizedLinear]
 
 
+class _SwiGLU:
+    """`down(silu(gate(x)) * up(x))` in one call: the gate and up rows as one [2I, .] tensor (a view when they
+    are adjacent slices of the fused checkpoint tensor, stacked once otherwise)."""
+
+    def forward_with_stream(self, x: torch.Tensor, stream=None) -> torch.Tensor:
+        g, u, d = self.gate_proj, self.up_proj, self.down_proj
+        if (g.mode, g.bits, g.group_size) != (u.mode, u.bits, u.group_size) or (g.mode, g.bits, g.group_size) != (d.mode, d.bits, d.group_size):
+            raise IronMLXError(_lib.ERR_INVALID, "the three projections of an expert must share one quantization format")
+        if g.mode == "nvfp4" and (g.global_scale or 1.0) != (u.global_scale or 1.0):
+            raise IronMLXError(_lib.ERR_INVALID, "gate_proj and up_proj carry different nvfp4 tensor scales")
+        fused = getattr(self, "_fused_gate_up", None)
+        if fused is None:
+            def both(a, b):
+                if a is None:
+                    return None
+                step = a.numel() * a.element_size()
+                if a.is_contiguous() and b.is_contiguous() and b.data_ptr() == a.data_ptr() + step:
+                    return a.as_strided((2 * a.shape[0],) + tuple(a.shape[1:]), a.stride())
+                return torch.cat([a, b], 0).contiguous()
+            fused = (both(g.weight, u.weight), both(g.scales, u.scales), both(g.biases, u.biases))
+            self._fused_gate_up = fused
+        return ops.expert_forward(x, fused[0], fused[1], fused[2], d.weight, d.scales, d.biases, g.group_size, g.bits,
+                                  g.mode, stream, g.global_scale, d.global_scale)
+
+
 @dataclass
-class MLP:
+class MLP(_SwiGLU):
     """SwiGLU MLP, `down(silu(gate(x)) * up(x))` (mlx/src/nn/mlp.rs:12-33);
     the shared expert of the block."""
     gate_proj: QuantizedLinear
@@ -91,7 +115,7 @@ class MLP:
 
 
 @dataclass
-class Expert:
+class Expert(_SwiGLU):
     """One routed expert (mlx/src/nn/moe.rs:11-33).  Its three projections are
     views into the fused [E, 2I, .] / [E, H, .] checkpoint tensors
     (mlx/src/model/qwen35.rs:661-776)."""
@@ -141,6 +165,11 @@ class MoEMLP:
             raise IronMLXError(_lib.ERR_INVALID, "router rows must equal the number of experts")
         if (shared_expert is None) != (shared_expert_gate is None):
             raise IronMLXError(_lib.ERR_INVALID, "shared_expert and shared_expert_gate go together")
+        if shared_expert is not None:
+            q = f.gate_up
+            for proj in (shared_expert.gate_proj, shared_expert.up_proj, shared_expert.down_proj):
+                if (proj.mode, proj.bits, proj.group_size) != (q.mode, q.bits, q.group_size):
+                    raise IronMLXError(_lib.ERR_INVALID, "the shared expert must use the routed experts' quantization format")
 
     # -- C structs ----------------------------------------------------------
     def config(self, path: Optional[str] = None) -> MoEConfig:
@@ -268,6 +297,14 @@ class MoEMLP:
         if self._workspace is not None:
             check(lib().imx_moe_status(self._workspace.data_ptr(), ops.stream_ptr(stream)))
 
+    def saturations(self, stream=None) -> int:
+        """Values the expert kernels had to clamp to the fp16 range since the last call (0: none)."""
+        if self._workspace is None:
+            return 0
+        n = C.c_longlong(0)
+        check(lib().imx_moe_saturations(self._workspace.data_ptr(), ops.stream_ptr(stream), C.byref(n)))
+        return int(n.value)
+
 
 class CapturedForward:
     """CUDA-graph replay of `MoEMLP.forward_with_stream` on static buffers:
@@ -327,6 +364,15 @@ class FusedExperts:
             raise IronMLXError(_lib.ERR_INVALID, "MoEMLP needs at least one expert")
         e0 = experts[0]
         q = e0.gate_proj
+        for e in experts:
+            for name, ref in (("gate_proj", e0.gate_proj), ("up_proj", e0.gate_proj), ("down_proj", e0.down_proj)):
+                p = getattr(e, name)
+                if (p.mode, p.bits, p.group_size) != (q.mode, q.bits, q.group_size):
+                    raise IronMLXError(_lib.ERR_INVALID, "experts to be fused must share one quantization format")
+                if p.mode == "nvfp4" and (p.global_scale or 1.0) != (ref.global_scale or 1.0):
+                    raise IronMLXError(_lib.ERR_INVALID,
+                                       "experts to be fused carry different nvfp4 tensor scales: quantize the stacked "
+                                       "tensor against one scale (the fused kernels take one per tensor)")
 
         def fuse(get):
             parts = [get(e) for e in experts]

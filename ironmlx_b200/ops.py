@@ -75,10 +75,69 @@ def quantized_matmul(x, w, scales, biases=None, transpose: bool = True, group_si
         raise IronMLXError(_lib.ERR_INVALID,
                            f"quantized_matmul: last dimension of x ({x.shape[-1]}) does not match {inner}")
     m_rows = x.numel() // inner
+    x = x.contiguous()
     y = torch.empty(*x.shape[:-1], n_out if transpose else in_dim, dtype=torch.bfloat16, device=x.device)
     qt = qtensor(w, scales, biases, global_scale)
-    check(lib().imx_quantized_matmul(x.data_ptr(), m_rows, C.byref(qt), n_out, in_dim, int(bool(transpose)),
+    if transpose:
+        # the layers' form: on the expert kernels where they take the shape (scratch cached per device and size)
+        nb = C.c_size_t(0)
+        check(lib().imx_quantized_matmul_scratch_bytes(m_rows, n_out, in_dim, g, b, m, C.byref(nb)))
+        ws = scratch(x.device, nb.value)
+        check(lib().imx_quantized_matmul_ws(x.data_ptr(), m_rows, C.byref(qt), n_out, in_dim, g, b, m, y.data_ptr(),
+                                            ws.data_ptr(), ws.numel(), stream_ptr(stream)))
+        return y
+    check(lib().imx_quantized_matmul(x.data_ptr(), m_rows, C.byref(qt), n_out, in_dim, 0,
                                      g, b, m, y.data_ptr(), stream_ptr(stream)))
+    return y
+
+
+_SCRATCH = {}
+
+
+def scratch(device, nbytes: int) -> torch.Tensor:
+    """A zero-filled device buffer of at least nbytes, kept per device (the layer calls' scratch; one stream of
+    calls at a time per device)."""
+    key = (device.type, device.index)
+    buf = _SCRATCH.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _SCRATCH[key] = buf
+    return buf
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """Dense `x @ W^T (+ b)` (mlx/src/nn/linear.rs:170-177), bf16 in and out, fp32 accumulation."""
+    _require_cuda(x, weight, bias)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.dim() != 2 or x.shape[-1] != weight.shape[1]:
+        raise IronMLXError(_lib.ERR_INVALID, "linear: x [.., in] and weight [out, in] must be bfloat16")
+    x = x.contiguous()
+    n_out, in_dim = weight.shape
+    y = torch.empty(*x.shape[:-1], n_out, dtype=torch.bfloat16, device=x.device)
+    check(lib().imx_linear(x.data_ptr(), x.numel() // in_dim, in_dim, weight.data_ptr(), n_out, _ptr(bias), y.data_ptr(),
+                           stream_ptr(stream)))
+    return y
+
+
+def expert_forward(x: torch.Tensor, gate_up_w, gate_up_s, gate_up_b, down_w, down_s, down_b, group_size=None, bits=None,
+                   mode: str = "affine", stream=None, gate_up_scale=None, down_scale=None) -> torch.Tensor:
+    """`down(silu(gate(x)) * up(x))` for one expert over all rows of x (mlx/src/nn/moe.rs:26-32,
+    mlx/src/nn/mlp.rs:27-33).  gate_up_*: [2I, .] with the gate rows first; down_*: [H, .]."""
+    g, b, m = resolve_format(group_size, bits, mode)
+    _require_cuda(x, gate_up_w, gate_up_s, gate_up_b, down_w, down_s, down_b)
+    hidden = x.shape[-1]
+    inter = gate_up_w.shape[-2] // 2
+    if x.dtype != torch.bfloat16 or down_w.shape[-2] != hidden:
+        raise IronMLXError(_lib.ERR_INVALID, "expert_forward: x must be bfloat16 [.., hidden] matching down [hidden, .]")
+    x = x.contiguous()
+    rows = x.numel() // hidden
+    y = torch.empty_like(x)
+    cfg = _lib.MoEConfig(hidden, 1, 1, inter, 0, 1, m, b, g, 0)
+    nb = C.c_size_t(0)
+    check(lib().imx_expert_scratch_bytes(C.byref(cfg), rows, C.byref(nb)))
+    ws = scratch(x.device, nb.value)
+    gu, dn = qtensor(gate_up_w, gate_up_s, gate_up_b, gate_up_scale), qtensor(down_w, down_s, down_b, down_scale)
+    check(lib().imx_expert_forward(C.byref(cfg), C.byref(gu), C.byref(dn), x.data_ptr(), rows, y.data_ptr(), ws.data_ptr(),
+                                   ws.numel(), stream_ptr(stream)))
     return y
 
 

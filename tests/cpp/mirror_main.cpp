@@ -117,6 +117,23 @@ int main(int argc, char** argv) {
         check_cuda(cudaMemcpy(ht.data(), yt.ptr, ht.size(), cudaMemcpyDeviceToHost));
         std::ofstream(dir + "/yt.bin", std::ios::binary).write(ht.data(), (std::streamsize)ht.size());
 
+        // MLP::forward_with_stream (the shared expert: three separate tensors, stacked once) and the dense router
+        // Linear::forward_with_stream on the same tokens
+        if (Is > 0) {
+            MLP mlp = *shared;
+            Array x2(x.ptr, {n, H}, Dtype::Bfloat16);
+            Array ym(dev.alloc((size_t)n * H * 2), {n, H}, Dtype::Bfloat16);
+            mlp.forward_with_stream(x2, ym, stream);
+            Array yl(dev.alloc((size_t)n * E * 2), {n, E}, Dtype::Bfloat16);
+            gate.forward_with_stream(x2, yl, stream);
+            check_cuda(cudaStreamSynchronize(stream));
+            std::vector<char> hm((size_t)n * H * 2), hl((size_t)n * E * 2);
+            check_cuda(cudaMemcpy(hm.data(), ym.ptr, hm.size(), cudaMemcpyDeviceToHost));
+            check_cuda(cudaMemcpy(hl.data(), yl.ptr, hl.size(), cudaMemcpyDeviceToHost));
+            std::ofstream(dir + "/ym.bin", std::ios::binary).write(hm.data(), (std::streamsize)hm.size());
+            std::ofstream(dir + "/yl.bin", std::ios::binary).write(hl.data(), (std::streamsize)hl.size());
+        }
+
         // error convention: a wrong shape must surface as ironmlx::Error with the library's message
         bool threw = false;
         try {

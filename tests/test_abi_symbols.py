@@ -7,11 +7,15 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 HEADER = os.path.join(ROOT, "include", "ironmlx_b200.h")
+TESTING_HEADER = os.path.join(ROOT, "include", "ironmlx_b200_testing.h")
 
 
 def declared_symbols():
+    """Every entry point of the boundary header, plus the test hooks of the testing header."""
     src = open(HEADER).read()
-    return sorted(set(re.findall(r"IMX_API\s+[\w\s\*]+?\b(imx_\w+)\s*\(", src)))
+    names = set(re.findall(r"IMX_API\s+[\w\s\*]+?\b(imx_\w+)\s*\(", src))
+    names |= set(re.findall(r"\b(imx_testing_\w+)\s*\(", open(TESTING_HEADER).read()))
+    return sorted(names)
 
 
 def test_header_declares_the_surface():

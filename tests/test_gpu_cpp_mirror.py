@@ -82,3 +82,10 @@ def test_cpp_mirror_matches_ctypes_path(cuda, tmp_path):
     yt = bf16_to_np(moe.forward_residual(t_bf16(x, cuda), inn.RMSNorm(t_bf16(lw, cuda), 1e-6)))
     yt_cpp = np.fromfile(os.path.join(d, "yt.bin"), dtype=F.bf16).astype(np.float32).reshape(yt.shape)
     assert np.array_equal(yt, yt_cpp)
+
+    ym = bf16_to_np(moe.shared_expert.forward_with_stream(t_bf16(x, cuda)))
+    ym_cpp = np.fromfile(os.path.join(d, "ym.bin"), dtype=F.bf16).astype(np.float32).reshape(ym.shape)
+    assert np.array_equal(ym, ym_cpp)
+    yl = bf16_to_np(moe.gate.forward_with_stream(t_bf16(x, cuda)))
+    yl_cpp = np.fromfile(os.path.join(d, "yl.bin"), dtype=F.bf16).astype(np.float32).reshape(yl.shape)
+    assert np.array_equal(yl, yl_cpp)
