@@ -25,10 +25,10 @@ const char* last_error() { return g_error.c_str(); }
 // Workspace of the fused forward.
 struct ForwardWs {
     int32_t* status;      // [16]: [0] device status word
-    int32_t* sched;       // [kSchedInts]
+    SchedWs sw;           // scheduler words and the tensor-map decode kernel's hand-off buffers
     int32_t* n_units;     // [4]: total, routed
-    float* partials;      // [kFlagWarps][256] hand-off slots of the decode kernels
-    float* gsum;          // [A + N, act_stride / 64] group sums of the SwiGLU rows (decode kernels)
+    float* partials;      // [kFlagWarps][256] hand-off slots of the stream-K decode kernels
+    float* psum;          // [A + N, act_stride / 16] sums of every 16 columns of the SwiGLU rows (tensor-map decode kernel)
     float* gsum_x;        // [N, H / 64] group sums of the fp16 copy of x
     float* inv_rms;          // [N] RMSNorm factor per token (decoder-layer tail)
     __nv_bfloat16* xn;       // [N, H] normalised input where the router cannot normalise its own tiles
@@ -65,7 +65,8 @@ ForwardWs carve_forward(const imx_moe_config& c, int n, void* base) {
     const int ns = c.shared_intermediate > 0 ? n : 0;
     Carver cv(base);
     w.status = cv.take<int32_t>(16);
-    w.sched = cv.take<int32_t>(kSchedInts);
+    w.max_units = max_units_for(A, c.num_experts, ns);
+    w.sw = carve_sched(cv, c.hidden, c.intermediate, c.shared_intermediate);
     w.n_units = cv.take<int32_t>(4);
     w.partials = cv.take<float>((size_t)kFlagWarps * 256);
     w.topk_idx = cv.take<int32_t>(A);
@@ -78,7 +79,6 @@ ForwardWs carve_forward(const imx_moe_config& c, int n, void* base) {
     w.inv_perm = cv.take<int32_t>(A);
     w.tok_of_slot = cv.take<int32_t>(A + ns);
     w.w_of_slot = cv.take<float>(A + ns);
-    w.max_units = max_units_for(A, c.num_experts, ns);
     w.units = cv.take<WorkUnit>(w.max_units);
     w.sort_scratch_bytes = sort_scratch_bytes(A, c.num_experts);
     w.sort_scratch = cv.take<uint8_t>(w.sort_scratch_bytes);
@@ -86,7 +86,7 @@ ForwardWs carve_forward(const imx_moe_config& c, int n, void* base) {
     w.act = cv.take<__half>((size_t)(A + ns) * w.act_stride);
     w.xs = cv.take<__half>((size_t)(A + ns) * c.hidden);
     w.rows = cv.take<float>((size_t)(A + ns) * c.hidden);
-    w.gsum = cv.take<float>((size_t)(A + ns) * (w.act_stride / 64 + 1));
+    w.psum = cv.take<float>((size_t)(A + ns) * (w.act_stride / 16 + 1));
     w.gsum_x = cv.take<float>((size_t)n * (c.hidden / 64 + 1));
     w.inv_rms = cv.take<float>((size_t)n);
     w.xn = cv.take<__nv_bfloat16>((size_t)n * c.hidden);
@@ -220,14 +220,14 @@ int run_experts(int path, const GroupedArgs& ga, cudaStream_t stream, cudaEvent_
 namespace {
 struct ExpertsWs {
     int32_t* status;     // [16]: [0] device status word (first in the scratch: imx_moe_status reads it there)
-    int32_t* sched;
+    SchedWs sw;
     int32_t* n_units;
     float* partials;
     WorkUnit* units;
     __half* act;
     __half* xperm;       // activations re-ordered for the decode kernels
     __half* xs;          // activations gathered into slot order (prefill path)
-    float* gsum;
+    float* psum;
     float* gsum_x;
     int max_units;
     size_t bytes;
@@ -236,15 +236,15 @@ ExpertsWs carve_experts(const imx_moe_config& c, int n_rows, int n_src_rows, voi
     ExpertsWs w = {};
     Carver cv(base);
     w.status = cv.take<int32_t>(16);
-    w.sched = cv.take<int32_t>(kSchedInts);
+    w.max_units = max_units_for(n_rows, c.num_experts, 0);
+    w.sw = carve_sched(cv, c.hidden, c.intermediate, 0);
     w.n_units = cv.take<int32_t>(4);
     w.partials = cv.take<float>((size_t)kFlagWarps * 256);
-    w.max_units = max_units_for(n_rows, c.num_experts, 0);
     w.units = cv.take<WorkUnit>(w.max_units);
     w.act = cv.take<__half>((size_t)n_rows * c.intermediate);
     w.xperm = cv.take<__half>((size_t)n_src_rows * c.hidden);
     w.xs = w.xperm;      // the prefill path uses one or the other
-    w.gsum = cv.take<float>((size_t)n_rows * (c.intermediate / 64 + 1));
+    w.psum = cv.take<float>((size_t)n_rows * (c.intermediate / 16 + 1));
     w.gsum_x = cv.take<float>((size_t)n_src_rows * (c.hidden / 64 + 1));
     w.bytes = align_up(cv.off, 256);
     return w;
@@ -372,7 +372,8 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     ex.units = ws.units;
     ex.n_units = ws.n_units;
     ex.unit_rows = unit_rows_for(path);
-    ex.sched = ws.sched;
+    ex.sched = ws.sw.sched;
+    ex.sched_ints = ws.sw.n_ints;
     IMX_TRY(launch_sort(ws.topk_idx, A, c.num_experts, ws.counts, ws.offsets, ws.perm, ws.inv_perm,
                         ws.sort_scratch, ws.sort_scratch_bytes, &ex, stream));
     IMX_CHECK_CUDA(mark(2));
@@ -385,9 +386,9 @@ static int forward_impl(const imx_moe_config* cfg, const imx_moe_weights* w, con
     ga.units = ws.units;
     ga.n_units = ws.n_units;
     ga.max_units = ws.max_units;
-    ga.sched = ws.sched;
+    use_sched(ga, ws.sw);
     ga.partials = ws.partials;
-    ga.gsum = ws.gsum;
+    ga.psum = ws.psum;
     ga.gsum_x = ws.gsum_x;
     ga.n_in_rows = n_tokens;
     ga.gsum_x_ready = sums_done ? 1 : 0;
@@ -603,7 +604,7 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
     int path;
     IMX_TRY(pick_path(c, set, (long)n_rows, &path));
     IMX_TRY(launch_build_units(offsets, num_experts, unit_rows_for(path), ws.units,
-                               ws.n_units, ws.sched, stream));
+                               ws.n_units, ws.sw.sched, ws.sw.n_ints, stream));
     GroupedArgs ga = {};
     ga.set = set;
     ga.in = (const __half*)x_f16;
@@ -624,9 +625,9 @@ int imx_moe_experts(const imx_moe_config* cfg, const imx_qtensor* gate_up, const
     ga.units = ws.units;
     ga.n_units = ws.n_units;
     ga.max_units = ws.max_units;
-    ga.sched = ws.sched;
+    use_sched(ga, ws.sw);
     ga.partials = ws.partials;
-    ga.gsum = ws.gsum;
+    ga.psum = ws.psum;
     ga.gsum_x = ws.gsum_x;
     ga.n_in_rows = n_rows;
     ga.n_rows_dev = offsets + num_experts;

@@ -186,7 +186,7 @@ ep_regroup_kernel(const int32_t* __restrict__ counts, int R, int E, int e_lo, in
 
 struct Common {
     int32_t* status;
-    int32_t* sched;
+    SchedWs sw;
     int32_t* n_units;
     float* partials;
 };
@@ -215,7 +215,7 @@ struct GatherWs {
     size_t sort_scratch_bytes;
     __half* act;
     float* rows;
-    float* gsum;
+    float* psum;
     float* partial;
     float* mine;
     int max_units, act_stride;
@@ -228,7 +228,8 @@ GatherWs carve_gather(const imx_ep_ctx& x, int n, void* base) {
     const int nA = n * x.world, A = nA * c.top_k, ns = c.shared_intermediate > 0 ? n : 0;
     Carver cv(base);
     w.c.status = cv.take<int32_t>(16);
-    w.c.sched = cv.take<int32_t>(kSchedInts);
+    w.max_units = max_units_for(A, x.e_loc, ns);
+    w.c.sw = carve_sched(cv, c.hidden, c.intermediate, c.shared_intermediate);
     w.c.n_units = cv.take<int32_t>(4);
     w.c.partials = cv.take<float>((size_t)kFlagWarps * 256);
     w.xg = cv.take<__nv_bfloat16>((size_t)nA * c.hidden);
@@ -251,14 +252,13 @@ GatherWs carve_gather(const imx_ep_ctx& x, int n, void* base) {
     w.inv_perm = cv.take<int32_t>(A);
     w.tok_of_slot = cv.take<int32_t>(A + ns);
     w.w_of_slot = cv.take<float>(A + ns);
-    w.max_units = max_units_for(A, x.e_loc, ns);
     w.units = cv.take<WorkUnit>(w.max_units);
     w.sort_scratch_bytes = sort_scratch_bytes(A, x.e_loc);
     w.sort_scratch = cv.take<uint8_t>(w.sort_scratch_bytes);
     w.act_stride = c.intermediate > c.shared_intermediate ? c.intermediate : c.shared_intermediate;
     w.act = cv.take<__half>((size_t)(A + ns) * w.act_stride);
     w.rows = cv.take<float>((size_t)(A + ns) * c.hidden);
-    w.gsum = cv.take<float>((size_t)(A + ns) * (w.act_stride / 64 + 1));
+    w.psum = cv.take<float>((size_t)(A + ns) * (w.act_stride / 16 + 1));
     w.partial = cv.take<float>((size_t)nA * c.hidden);
     w.mine = cv.take<float>((size_t)n * c.hidden);
     w.bytes = align_up(cv.off, 256);
@@ -303,7 +303,7 @@ A2aWs carve_a2a(const imx_ep_ctx& x, int n, void* base) {
     w.cap = A * x.world;
     Carver cv(base);
     w.c.status = cv.take<int32_t>(16);
-    w.c.sched = cv.take<int32_t>(kSchedInts);
+    w.c.sw = carve_sched(cv, 0, 0, 0);        // this schedule runs the tensor-core kernels only: no hand-off buffers
     w.c.n_units = cv.take<int32_t>(4);
     w.c.partials = cv.take<float>((size_t)kFlagWarps * 256);
     w.topk_idx = cv.take<int32_t>(A);
@@ -392,7 +392,8 @@ int forward_gathered(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, i
     ex.units = ws.units;
     ex.n_units = ws.c.n_units;
     ex.unit_rows = unit_rows_for(path);
-    ex.sched = ws.c.sched;
+    ex.sched = ws.c.sw.sched;
+    ex.sched_ints = ws.c.sw.n_ints;
     IMX_TRY(launch_sort(ws.ids_local, A, x.e_loc, ws.counts, ws.offsets, ws.perm, ws.inv_perm, ws.sort_scratch,
                         ws.sort_scratch_bytes, &ex, stream));
     GroupedArgs ga = {};
@@ -403,9 +404,9 @@ int forward_gathered(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, i
     ga.units = ws.units;
     ga.n_units = ws.c.n_units;
     ga.max_units = ws.max_units;
-    ga.sched = ws.c.sched;
+    use_sched(ga, ws.c.sw);
     ga.partials = ws.c.partials;
-    ga.gsum = ws.gsum;
+    ga.psum = ws.psum;
     ga.gsum_x = ws.gsum_x;
     ga.n_in_rows = nA;
     ga.gsum_x_ready = sums_done ? 1 : 0;
@@ -522,8 +523,8 @@ int forward_a2a(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, int n,
     ep_regroup_kernel<<<x.e_loc + 1, 256, 0, stream>>>(ws.all_counts, R, E, x.rank * x.e_loc, x.e_loc, ws.cap, n, has_shared ? 1 : 0,
                                                      ws.row_index, ws.offsets2); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
-    IMX_TRY(launch_build_units(ws.offsets2, x.e_loc + (has_shared ? 1 : 0), unit_rows_for(path), ws.units, ws.c.n_units, ws.c.sched,
-                               stream, has_shared ? x.e_loc : -1));
+    IMX_TRY(launch_build_units(ws.offsets2, x.e_loc + (has_shared ? 1 : 0), unit_rows_for(path), ws.units, ws.c.n_units, ws.c.sw.sched,
+                               ws.c.sw.n_ints, stream, has_shared ? x.e_loc : -1));
     // 6. the experts: rows come in through row_index, results leave through it (row j of ret_buf is the result
     //    of row j of recv_buf)
     GroupedArgs ga = {};
@@ -535,7 +536,7 @@ int forward_a2a(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, int n,
     ga.units = ws.units;
     ga.n_units = ws.c.n_units;
     ga.max_units = ws.max_units;
-    ga.sched = ws.c.sched;
+    use_sched(ga, ws.c.sw);
     ga.partials = ws.c.partials;
     ga.n_in_rows = ws.cap + n;
     ga.act = ws.act;

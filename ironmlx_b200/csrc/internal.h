@@ -28,9 +28,19 @@ struct Order16 {
 
 // Ints cleared by the sort stage before every pass of the expert kernels:
 // [0, 8) scheduler counters, then one "partial ready" flag per warp of the two
-// decode kernels (stream-K hand-off), kFlagWarps each.
+// stream-K decode kernels (kFlagWarps each), then the arrival counters of the
+// tensor-map decode kernel's cut tile pairs (TmapRoom::pair_slots of them).
 constexpr int kFlagWarps = 4096;
-constexpr int kSchedInts = 8 + 2 * kFlagWarps;
+constexpr int kSchedFixed = 8 + 2 * kFlagWarps;
+// Room of the tensor-map decode kernel's hand-off buffers: tile pairs whose reduction goes out in several
+// chunks (only the last pairs of a launch do) and chunks per pair.
+constexpr int kTmapFinePairs = 4096;
+struct TmapRoom {
+    int pair_slots;
+    int cut;
+};
+TmapRoom decode_tmap_room(int n_in, int n_mid, int x_mid);
+inline int sched_ints(const TmapRoom& r) { return kSchedFixed + r.pair_slots; }
 constexpr int kUnitRows = 8;       // slots per decode work unit (the n=8 side of the MMA)
 
 struct SortExtras {
@@ -45,6 +55,7 @@ struct SortExtras {
     int32_t* n_units = nullptr;
     int unit_rows = kUnitRows;
     int32_t* sched = nullptr;
+    int sched_ints = kSchedFixed;     // words of sched to clear
 };
 
 // Workspace of the split-K router (decode sizes): all pointers together or none.
@@ -107,9 +118,12 @@ struct GroupedArgs {
     const WorkUnit* units;
     const int32_t* n_units;
     int max_units;
-    int32_t* sched;                // [kSchedInts]: counters, then the hand-off flags
-    float* partials;               // [kFlagWarps][8][32] fp32 hand-off slots (decode kernels)
-    float* gsum;                   // [n_slots, act_stride / 64] fp32 group sums of the SwiGLU rows (tensor-map decode kernel)
+    int32_t* sched;                // [sched_ints(room)]: counters, the stream-K hand-off flags, the pair counters
+    float* partials;               // [kFlagWarps][8][32] fp32 hand-off slots (stream-K decode kernels)
+    float* psum;                   // [n_slots, act_stride / 16] fp32 sums of every 16 columns of the SwiGLU rows (tensor-map decode kernel)
+    int32_t* pair_count;           // tensor-map decode kernel: arrivals per cut tile pair (sched + kSchedFixed), zero between launches
+    float* pair_partials;          // ... and [pair_slots][pair_cut][8][32] fp32 partial sums of the pairs' chunks
+    int pair_slots, pair_cut;      // room of the two (TmapRoom)
     float* gsum_x;                 // [n_in_rows, n_in / 64] fp32 group sums of the rows of `in`
     int n_in_rows;                 // rows of `in`
     const int32_t* n_rows_dev;     // device-side count of rows of `in` that are in use (nullptr: all n_in_rows)
@@ -139,7 +153,7 @@ constexpr int kPrefillUnitRows = 256;
 // Prefill path for every tensor-core format: the dequantized weights are the A operand, handed to the MMA
 // through tensor memory.  variant 0: as shipped; 1: one weight tile per activation tile and streamed
 // activations everywhere; 2: the dequantized tile through shared memory (1 and 2 are cross-checks).
-bool prefill_tc_supported(const ExpertSet& s);
+bool prefill_tc_supported(const ExpertSet& s, bool second_only = false);
 int launch_prefill_tc(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid = nullptr, int variant = 0);
 // The current device: its ordinal and SM count (cached per device).
 struct DeviceInfo {
@@ -175,7 +189,7 @@ int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t
 // Builds the unit list for a caller-given offsets array (stage-level API).  extra_from >= 0: the units of that
 // (last) expert are listed as the extra expert's.
 int launch_build_units(const int32_t* offsets, int E, int unit_rows, WorkUnit* units, int32_t* n_units,
-                       int32_t* sched, cudaStream_t stream, int extra_from = -1);
+                       int32_t* sched, int sched_ints, cudaStream_t stream, int extra_from = -1);
 
 int launch_dequantize(const QMat& w, int rows, int in, QFormat f, int out_dtype, void* out,
                       cudaStream_t stream);
@@ -201,6 +215,29 @@ struct Carver {
         return p;
     }
 };
+
+// Scheduler words and the tensor-map decode kernel's hand-off buffers of a workspace, carved together.
+struct SchedWs {
+    int32_t* sched;
+    int n_ints;
+    float* pair_partials;
+    TmapRoom room;
+};
+inline SchedWs carve_sched(Carver& cv, int n_in, int n_mid, int x_mid) {
+    SchedWs w;
+    w.room = decode_tmap_room(n_in, n_mid, x_mid);
+    w.n_ints = sched_ints(w.room);
+    w.sched = cv.take<int32_t>((size_t)w.n_ints);
+    w.pair_partials = cv.take<float>((size_t)w.room.pair_slots * w.room.cut * 256);
+    return w;
+}
+inline void use_sched(GroupedArgs& ga, const SchedWs& w) {
+    ga.sched = w.sched;
+    ga.pair_count = w.sched + kSchedFixed;
+    ga.pair_partials = w.pair_partials;
+    ga.pair_slots = w.room.pair_slots;
+    ga.pair_cut = w.room.cut;
+}
 int check_config(const imx_moe_config* c, QFormat* f);
 int make_expert_set(const imx_moe_config& c, const QFormat& f, const imx_qtensor& gate_up, const imx_qtensor& down,
                     int num_experts, const imx_moe_weights* shared, ExpertSet* out);

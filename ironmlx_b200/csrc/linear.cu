@@ -22,31 +22,62 @@ namespace imx {
 
 namespace {
 
-// fp16 copy of bf16 rows in the 16-value block order the expert kernels of a format read; pairs 1 and 3
-// of every 8 stored values are multiplied by pair_scale_odd (the tensor-map decode kernel's convention).
-__global__ void convert_rows_kernel(const __nv_bfloat16* __restrict__ src, int cols, __half* __restrict__ dst,
-                                    const Order16 order) {
-    const size_t r = blockIdx.x;
-    const __nv_bfloat16* s = src + r * cols;
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
-        const float v = __bfloat162float(s[(i & ~15) + order.o[i & 15]]);
-        dst[r * cols + i] = __float2half_rn((i & 2) ? v * order.pair_scale_odd : v);
+// Everything a one-expert launch needs, in one kernel.  Blocks 0 .. m-1: the fp16 copy of a bf16 row in the
+// 16-value block order the expert kernels of a format read (pairs 1 and 3 of every 8 stored values multiplied
+// by pair_scale_odd, the tensor-map decode kernel's convention).  Block m: the identity slot order, the work
+// units of the single expert (balanced, at most unit_rows slots each) and cleared scheduler words.
+__global__ void __launch_bounds__(256)
+prepare_one_kernel(const __nv_bfloat16* __restrict__ src, int m, int cols, __half* __restrict__ dst, const Order16 order,
+                   int unit_rows, int32_t* __restrict__ offsets, int32_t* __restrict__ ident, WorkUnit* __restrict__ units,
+                   int32_t* __restrict__ n_units, int32_t* __restrict__ sched, int sched_ints, float* __restrict__ psum) {
+    if ((int)blockIdx.x < m) {
+        const size_t r = blockIdx.x;
+        const __nv_bfloat16* s = src + r * cols;
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+            const float v = __bfloat162float(s[(i & ~15) + order.o[i & 15]]);
+            dst[r * cols + i] = __float2half_rn((i & 2) ? v * order.pair_scale_odd : v);
+        }
+        if (psum != nullptr) {
+            // sums of every 16 values of the row as the expert kernels will read them (the tensor-map decode
+            // kernel's second product takes its group sums from these)
+            __syncthreads();
+            const float unscale = 1.f / order.pair_scale_odd;
+            for (int b = threadIdx.x; b < cols / 16; b += blockDim.x) {
+                float acc = 0.f;
+                for (int i = 0; i < 16; ++i) {
+                    const float v = __half2float(dst[r * cols + b * 16 + i]);
+                    acc += (i & 2) ? v * unscale : v;
+                }
+                psum[r * (cols / 16) + b] = acc;
+            }
+        }
+        return;
     }
-}
-
-// offsets = [0, m]; ident[i] = i
-__global__ void one_expert_kernel(int m, int32_t* __restrict__ offsets, int32_t* __restrict__ ident) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i == 0) {
+    const int tid = threadIdx.x;
+    const int nu = (m + unit_rows - 1) / unit_rows;
+    int per = (m + nu - 1) / nu;                       // equal shares, rounded up to whole blocks of 16 slots
+    per = (per + 15) & ~15;
+    if (per > unit_rows) per = unit_rows;
+    for (int i = tid; i < m; i += blockDim.x) ident[i] = i;
+    for (int c = tid; c < nu; c += blockDim.x) {
+        WorkUnit u;
+        u.expert = 0;
+        u.slot0 = c * per;
+        u.rows = min(per, m - c * per);
+        u.pad = 0;
+        units[c] = u;
+    }
+    for (int i = tid; i < sched_ints; i += blockDim.x) sched[i] = 0;
+    if (tid == 0) {
         offsets[0] = 0;
         offsets[1] = m;
+        n_units[0] = n_units[1] = nu;
     }
-    if (i < m) ident[i] = i;
 }
 
 struct OneWs {
     int32_t* status;
-    int32_t* sched;
+    SchedWs sw;
     int32_t* n_units;
     float* partials;
     int32_t* offsets;     // [2]
@@ -54,7 +85,7 @@ struct OneWs {
     WorkUnit* units;
     __half* x16;          // [m, in]
     __half* act;          // [m, mid]      (expert forward)
-    float* gsum;          // [m, K / 64 + 1]
+    float* psum;          // [m, K / 16 + 1]
     float* gsum_x;        // [m, in / 64 + 1]
     float* rows;          // [m, out] fp32 (or fp16 in the same buffer)
     int max_units;
@@ -65,17 +96,18 @@ OneWs carve_one(int m, int in, int mid, int out, void* base) {
     OneWs w = {};
     Carver cv(base);
     w.status = cv.take<int32_t>(16);
-    w.sched = cv.take<int32_t>(kSchedInts);
+    w.max_units = max_units_for(m, 1, 0);
+    // as the second product alone the matrix is [out, in]: reduction over `in`, `out` output rows
+    w.sw = mid > 0 ? carve_sched(cv, in, mid, 0) : carve_sched(cv, out, in, 0);
     w.n_units = cv.take<int32_t>(4);
     w.partials = cv.take<float>((size_t)kFlagWarps * 256);
     w.offsets = cv.take<int32_t>(4);
     w.ident = cv.take<int32_t>(m);
-    w.max_units = max_units_for(m, 1, 0);
     w.units = cv.take<WorkUnit>(w.max_units);
     w.x16 = cv.take<__half>((size_t)m * in);
     if (mid > 0) w.act = cv.take<__half>((size_t)m * mid);
     const int kmax = mid > in ? mid : in;
-    w.gsum = cv.take<float>((size_t)m * (kmax / 64 + 1));
+    w.psum = cv.take<float>((size_t)m * (kmax / 16 + 1));
     w.gsum_x = cv.take<float>((size_t)m * (in / 64 + 1));
     w.rows = cv.take<float>((size_t)m * out);
     w.bytes = align_up(cv.off, 256);
@@ -114,9 +146,9 @@ int qmm_set(const imx_qtensor& w, int n_out, int in, const QFormat& f, ExpertSet
 
 // Which kernel runs a [m, in] x [n_out, in]^T product alone; IMX_PATH_GENERIC = none of the expert kernels.
 int qmm_path(const ExpertSet& s, int m) {
-    if (m >= 32 && prefill_tc_supported(s)) return IMX_PATH_PREFILL;
+    if (m >= 32 && prefill_tc_supported(s, true)) return IMX_PATH_PREFILL;
     if (m <= 256 && (decode_tmap_supported(s) || decode_mma_supported(s) || decode_fp_supported(s))) return IMX_PATH_DECODE;
-    if (prefill_tc_supported(s)) return IMX_PATH_PREFILL;
+    if (prefill_tc_supported(s, true)) return IMX_PATH_PREFILL;
     return IMX_PATH_GENERIC;
 }
 
@@ -239,12 +271,12 @@ int imx_quantized_matmul_ws(const void* x, int m, const imx_qtensor* w, int n_ou
     path_block_order(path, f, o);
     Order16 order;
     for (int i = 0; i < 16; ++i) order.o[i] = (int8_t)o[i];
-    order.pair_scale_odd = path == IMX_PATH_DECODE && decode_tmap_supported(set) ? 0.0625f : 1.f;
-    convert_rows_kernel<<<m, 256, 0, stream>>>((const __nv_bfloat16*)x, in, ws.x16, order); IMX_LAUNCHED();
+    const bool tmap_second = path == IMX_PATH_DECODE && decode_tmap_supported(set);
+    order.pair_scale_odd = tmap_second ? 0.0625f : 1.f;
+    prepare_one_kernel<<<m + 1, 256, 0, stream>>>((const __nv_bfloat16*)x, m, in, ws.x16, order, unit_rows_for(path), ws.offsets,
+                                                  ws.ident, ws.units, ws.n_units, ws.sw.sched, ws.sw.n_ints,
+                                                  tmap_second ? ws.psum : nullptr); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
-    one_expert_kernel<<<(m + 255) / 256, 256, 0, stream>>>(m, ws.offsets, ws.ident); IMX_LAUNCHED();
-    IMX_CHECK_CUDA(cudaGetLastError());
-    IMX_TRY(launch_build_units(ws.offsets, 1, unit_rows_for(path), ws.units, ws.n_units, ws.sched, stream));
     GroupedArgs ga = {};
     ga.set = set;
     ga.second_only = 1;
@@ -252,9 +284,9 @@ int imx_quantized_matmul_ws(const void* x, int m, const imx_qtensor* w, int n_ou
     ga.units = ws.units;
     ga.n_units = ws.n_units;
     ga.max_units = ws.max_units;
-    ga.sched = ws.sched;
+    use_sched(ga, ws.sw);
     ga.partials = ws.partials;
-    ga.gsum = ws.gsum;
+    ga.psum = ws.psum;
     ga.act = ws.x16;                 // the second product reads its activations here
     ga.act_stride = in;
     ga.out = ws.rows;
@@ -295,11 +327,10 @@ int imx_expert_forward(const imx_moe_config* cfg, const imx_qtensor* gate_up, co
     for (int i = 0; i < 16; ++i) order.o[i] = (int8_t)o[i];
     const bool tmap = path == IMX_PATH_DECODE && decode_tmap_supported(set);
     order.pair_scale_odd = tmap ? 0.0625f : 1.f;
-    convert_rows_kernel<<<m, 256, 0, stream>>>((const __nv_bfloat16*)x, c.hidden, ws.x16, order); IMX_LAUNCHED();
+    prepare_one_kernel<<<m + 1, 256, 0, stream>>>((const __nv_bfloat16*)x, m, c.hidden, ws.x16, order, unit_rows_for(path),
+                                                  ws.offsets, ws.ident, ws.units, ws.n_units, ws.sw.sched, ws.sw.n_ints,
+                                                  nullptr); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
-    one_expert_kernel<<<(m + 255) / 256, 256, 0, stream>>>(m, ws.offsets, ws.ident); IMX_LAUNCHED();
-    IMX_CHECK_CUDA(cudaGetLastError());
-    IMX_TRY(launch_build_units(ws.offsets, 1, unit_rows_for(path), ws.units, ws.n_units, ws.sched, stream));
     const bool rows_f16 = is_prefill(path);
     GroupedArgs ga = {};
     ga.set = set;
@@ -308,9 +339,9 @@ int imx_expert_forward(const imx_moe_config* cfg, const imx_qtensor* gate_up, co
     ga.units = ws.units;
     ga.n_units = ws.n_units;
     ga.max_units = ws.max_units;
-    ga.sched = ws.sched;
+    use_sched(ga, ws.sw);
     ga.partials = ws.partials;
-    ga.gsum = ws.gsum;
+    ga.psum = ws.psum;
     ga.gsum_x = ws.gsum_x;
     ga.n_in_rows = m;
     ga.act = ws.act;

@@ -980,13 +980,14 @@ extern "C" IMX_API int imx_debug_tc_prof(unsigned long long* out32) {
 }
 #endif
 
-bool prefill_tc_supported(const ExpertSet& s) {
+bool prefill_tc_supported(const ExpertSet& s, bool second_only) {
     const QFormat& f = s.fmt;
     if (fmt_index(f) < 0) return false;
     if (log2_exact(f.group) < 0 || f.group > 128 || f.group < 16) return false;
     if (f.mode == IMX_MODE_AFFINE && f.group < 32) return false;
     if (s.n_in % 128 || s.n_mid % 64) return false;
-    if (!k_ok(s.n_in, f) || !k_ok(s.n_mid, f)) return false;
+    // the second product alone never reduces over n_in (a plain quantized matmul with any number of output rows)
+    if ((!second_only && !k_ok(s.n_in, f)) || !k_ok(s.n_mid, f)) return false;
     if (s.has_extra && (s.x_mid % 64 || !k_ok(s.x_mid, f))) return false;
     return true;
 }
@@ -995,7 +996,7 @@ bool prefill_tc_supported(const ExpertSet& s) {
 // activation panel in the second where it fits), 1 = tensor-memory operand, 128-slot tiles and streamed
 // activations everywhere, 2 = as 1 with the dequantized tile in shared memory (1, 2: cross-checks).
 int launch_prefill_tc(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid, int variant) {
-    IMX_REQUIRE(prefill_tc_supported(a.set), "prefill path: format/shape not supported");
+    IMX_REQUIRE(prefill_tc_supported(a.set, a.second_only != 0), "prefill path: format/shape not supported");
     IMX_REQUIRE((a.row_index == nullptr || a.xs != nullptr || a.second_only) && a.n_slots > 0,
                 "prefill path: slot-ordered activation buffer missing");
     if (a.max_units == 0) return IMX_OK;

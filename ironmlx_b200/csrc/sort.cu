@@ -145,14 +145,15 @@ struct SortAux {
     WorkUnit* units;         // work units of `unit_rows` rows
     int32_t* n_units;
     int unit_rows;
-    int32_t* sched;          // scheduler counters to clear (kSchedInts ints)
+    int32_t* sched;          // scheduler words to clear
+    int sched_ints;
 };
 
 __device__ void emit_aux(const SortAux& aux, const int32_t* __restrict__ perm, const int* s_off,
                          int E, int A, int* s_warp) {
     const int tid = threadIdx.x;
     if (aux.sched != nullptr)
-        for (int i = tid; i < kSchedInts; i += kSortThreads) aux.sched[i] = 0;
+        for (int i = tid; i < aux.sched_ints; i += kSortThreads) aux.sched[i] = 0;
     if (aux.tok_of_slot != nullptr) {
         const int total = s_off[E];
         for (int j = tid; j < total; j += kSortThreads) {
@@ -392,7 +393,7 @@ sort_place_kernel(const int32_t* __restrict__ ids, int A, int E, const int32_t* 
 // the positions; also clears the scheduler words.
 static __global__ void __launch_bounds__(kSortThreads)
 build_units_kernel(const int32_t* __restrict__ offsets, int E, int unit_rows, WorkUnit* __restrict__ units,
-                   int32_t* __restrict__ n_units, int32_t* __restrict__ sched, int extra_from) {
+                   int32_t* __restrict__ n_units, int32_t* __restrict__ sched, int sched_ints, int extra_from) {
     __shared__ int s_warp[33];
     const int tid = threadIdx.x;
     int cnt = 0, pos0 = 0;
@@ -417,13 +418,13 @@ build_units_kernel(const int32_t* __restrict__ offsets, int E, int unit_rows, Wo
     // lists it as the last "expert") follow
     if (extra_from >= 0 ? tid == extra_from : tid == 0) n_units[1] = extra_from >= 0 ? base : total;
     if (sched != nullptr)
-        for (int i = tid; i < kSchedInts; i += kSortThreads) sched[i] = 0;
+        for (int i = tid; i < sched_ints; i += kSortThreads) sched[i] = 0;
 }
 
 int launch_build_units(const int32_t* offsets, int E, int unit_rows, WorkUnit* units, int32_t* n_units,
-                       int32_t* sched, cudaStream_t stream, int extra_from) {
+                       int32_t* sched, int sched_ints, cudaStream_t stream, int extra_from) {
     IMX_REQUIRE(E >= 1 && E < kSortThreads, "build_units: num_experts (%d) must be in 1..%d", E, kSortThreads - 1);
-    build_units_kernel<<<1, kSortThreads, 0, stream>>>(offsets, E, unit_rows, units, n_units, sched, extra_from); IMX_LAUNCHED();
+    build_units_kernel<<<1, kSortThreads, 0, stream>>>(offsets, E, unit_rows, units, n_units, sched, sched_ints, extra_from); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }
@@ -487,6 +488,7 @@ int launch_sort(const int32_t* ids, int A, int E, int32_t* counts, int32_t* offs
         aux.n_units = ex->n_units;
         aux.unit_rows = ex->unit_rows > 0 ? ex->unit_rows : 8;
         aux.sched = ex->sched;
+        aux.sched_ints = ex->sched_ints;
         IMX_REQUIRE(aux.units == nullptr || E + 1 <= kSortThreads, "sort: too many experts for the unit list");
     }
     const size_t smem_fused = ((size_t)kSortWarps * E + E + E + 1 + 33) * sizeof(int);

@@ -96,8 +96,12 @@ class _SwiGLU:
                 if a is None:
                     return None
                 step = a.numel() * a.element_size()
-                if a.is_contiguous() and b.is_contiguous() and b.data_ptr() == a.data_ptr() + step:
-                    return a.as_strided((2 * a.shape[0],) + tuple(a.shape[1:]), a.stride())
+                # adjacent slices of ONE tensor (same storage, which also has to hold both): neighbours in
+                # memory that belong to two allocations are not a view of anything
+                same = (a.untyped_storage().data_ptr() == b.untyped_storage().data_ptr()
+                        and a.untyped_storage().nbytes() >= a.storage_offset() * a.element_size() + 2 * step)
+                if same and a.is_contiguous() and b.is_contiguous() and b.data_ptr() == a.data_ptr() + step:
+                    return a.as_strided((2 * a.shape[0],) + tuple(a.shape[1:]), a.stride(), a.storage_offset())
                 return torch.cat([a, b], 0).contiguous()
             fused = (both(g.weight, u.weight), both(g.scales, u.scales), both(g.biases, u.biases))
             self._fused_gate_up = fused
