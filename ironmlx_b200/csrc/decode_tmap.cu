@@ -297,12 +297,10 @@ decode_first_kernel(const GroupedArgs a, const int ppu_r, const int ppu_x, const
             const uint32_t bar = bars + 8 * slot;
             const uint32_t wdst = wbuf + slot * kWBytes;
             mbar_expect_tx(bar, with_scales ? kWBytes + kSBytes : kWBytes);
-            // The routed experts' weights, scales and biases are read once per step: first in line for
-            // eviction, so that the stream does not push the activations, sums and hand-off slots out of L2
-            // (8 % of the c2 step).  The extra expert's are read again by every one of its units: kept.
+            // weights, scales and biases are read once per step: first in line for eviction, so that the
+            // stream does not push the activations, sums and hand-off slots out of L2 (8 % of the c2 step)
             uint64_t policy;
-            if (fc.extra) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
-            else asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+            asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
             tma_load_2d_hint(wdst, &maps.w[f_map0], fc.st * 128, f_row0, bar, policy);
             tma_load_2d_hint(wdst + 2048, &maps.w[f_map1], fc.st * 128, f_row1, bar, policy);
             if (with_scales) {

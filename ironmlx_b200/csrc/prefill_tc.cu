@@ -941,6 +941,7 @@ int configure() {
     IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<true, FMT, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
     IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<false, FMT, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
     IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<false, FMT, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<false, FMT, true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
     IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<true, FMT, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
     IMX_CHECK_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<false, FMT, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
     return IMX_OK;
@@ -965,6 +966,7 @@ int launch_fmt(const GroupedArgs& a, const Plan& gu, const Plan& dn, bool ts, co
     }
     if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
     if (!ts) prefill_tc_kernel<false, FMT, false, false, false><<<sms, kThreadsTc, dn.smem, stream>>>(a, dn.p, mdn);
+    else if (dn.wide) prefill_tc_kernel<false, FMT, true, true, false><<<sms, kThreadsTc, dn.smem, stream>>>(a, dn.p, mdn);
     else if (dn.xr) prefill_tc_kernel<false, FMT, true, false, true><<<sms, kThreadsTc, dn.smem, stream>>>(a, dn.p, mdn);
     else prefill_tc_kernel<false, FMT, true, false, false><<<sms, kThreadsTc, dn.smem, stream>>>(a, dn.p, mdn);
     IMX_LAUNCHED();
@@ -992,9 +994,9 @@ bool prefill_tc_supported(const ExpertSet& s, bool second_only) {
     return true;
 }
 
-// variant: 0 = the shipped configuration (tensor-memory operand, 256-slot tiles in the first product, resident
-// activation panel in the second where it fits), 1 = tensor-memory operand, 128-slot tiles and streamed
-// activations everywhere, 2 = as 1 with the dequantized tile in shared memory (1, 2: cross-checks).
+// variant: 0 = the shipped configuration (tensor-memory operand, 256-slot tiles in both products), 1 =
+// tensor-memory operand, 128-slot tiles and streamed activations everywhere, 2 = as 1 with the dequantized
+// tile in shared memory (1, 2: cross-checks).
 int launch_prefill_tc(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid, int variant) {
     IMX_REQUIRE(prefill_tc_supported(a.set, a.second_only != 0), "prefill path: format/shape not supported");
     IMX_REQUIRE((a.row_index == nullptr || a.xs != nullptr || a.second_only) && a.n_slots > 0,
@@ -1048,7 +1050,9 @@ int launch_prefill_tc(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid
     Plan gu = {}, dn = {};
     if (!a.second_only && !(variant == 0 && plan(s.n_in, s.n_in, true, false, &gu)))
         IMX_REQUIRE(plan(s.n_in, s.n_in, false, false, &gu), "prefill path: sizes exceed shared memory");
-    if (!(variant == 0 && plan(mid_max, mid_min, false, true, &dn)))
+    // second product: 256-slot tiles with streamed activations as well (c3: 276 us against 377 us with 128-slot
+    // tiles and the activation panel resident); the resident panel where the wide stages do not fit
+    if (!(variant == 0 && (plan(mid_max, mid_min, true, false, &dn) || plan(mid_max, mid_min, false, true, &dn))))
         IMX_REQUIRE(plan(mid_max, mid_min, false, false, &dn), "prefill path: sizes exceed shared memory");
     gu.p.nt_r = s.n_mid / 64;
     gu.p.nt_x = x_mid / 64;
