@@ -129,11 +129,29 @@ __global__ void gather_rows_kernel(const uint32_t* __restrict__ src, const int32
     const int j = blockIdx.x;
     const uint32_t* s = src + (size_t)index[j] * words;
     uint32_t* d = dst + (size_t)j * words;
-    if ((words & 3) == 0) {
-        for (int i = threadIdx.x; i < words / 4; i += blockDim.x)
-            reinterpret_cast<uint4*>(d)[i] = __ldg(reinterpret_cast<const uint4*>(s) + i);
-    } else {
-        for (int i = threadIdx.x; i < words; i += blockDim.x) d[i] = __ldg(s + i);
+    for (int i = threadIdx.x; i < words; i += blockDim.x) d[i] = __ldg(s + i);
+}
+
+// The same for rows that are multiples of 16 bytes: a warp per row at a time, eight 16-byte pieces per lane
+// in flight before the first is stored (one small CTA per row spends its time being launched).
+constexpr int kGatherWarps = 8;
+__global__ void __launch_bounds__(kGatherWarps * 32)
+gather_rows16_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ index, int n_rows, int pieces,
+                     uint4* __restrict__ dst) {
+    const int lane = threadIdx.x & 31;
+    const int stride = gridDim.x * kGatherWarps;
+    for (int j = blockIdx.x * kGatherWarps + (threadIdx.x >> 5); j < n_rows; j += stride) {
+        const uint4* s = src + (size_t)__ldg(index + j) * pieces;
+        uint4* d = dst + (size_t)j * pieces;
+        for (int i0 = lane; i0 < pieces; i0 += 32 * 8) {
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (i0 + u * 32 < pieces) v[u] = __ldg(s + i0 + u * 32);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (i0 + u * 32 < pieces) d[i0 + u * 32] = v[u];
+        }
     }
 }
 
@@ -146,6 +164,14 @@ int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t
                 "gather_rows: 16-byte rows need 16-byte aligned buffers");
     if (n_rows == 0) return IMX_OK;
     const int words = (int)(row_bytes / 4);
+    if (row_bytes % 16 == 0) {
+        int grid = ceil_div(n_rows, kGatherWarps);
+        if (grid > 148 * 8) grid = 148 * 8;
+        gather_rows16_kernel<<<grid, kGatherWarps * 32, 0, stream>>>((const uint4*)src, index, n_rows, (int)(row_bytes / 16),
+                                                                    (uint4*)dst); IMX_LAUNCHED();
+        IMX_CHECK_CUDA(cudaGetLastError());
+        return IMX_OK;
+    }
     const int threads = words >= 1024 ? 256 : (words >= 128 ? 128 : 32);
     gather_rows_kernel<<<n_rows, threads, 0, stream>>>((const uint32_t*)src, index, words, (uint32_t*)dst); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());

@@ -14,7 +14,7 @@
 // plus x; the stage is latency-bound, not bandwidth-bound.
 #include <cooperative_groups.h>
 
-#include "internal.h"
+#include "decode_common.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -23,6 +23,49 @@ namespace imx {
 namespace {
 
 constexpr int kRouteThreads = 256;
+
+// Block order of the fp16 copy by code width (0: rows stay as they are): position p of a block of 16 takes
+// value order16<BITS>(p) of the source block.
+template <int BITS>
+__host__ __device__ constexpr int order16(int p) {
+    if constexpr (BITS == 0) return p;
+    else return decode::Codec<BITS>::order(p);
+}
+// Which of them `order` is, or -1.
+inline int order_bits(const Order16& order) {
+    const int widths[4] = {0, 4, 8, 2};
+    for (int w = 0; w < 4; ++w) {
+        bool same = true;
+        for (int i = 0; i < 16; ++i) {
+            const int want = widths[w] == 0 ? order16<0>(i) : (widths[w] == 4 ? order16<4>(i) : (widths[w] == 8 ? order16<8>(i) : order16<2>(i)));
+            same = same && order.o[i] == want;
+        }
+        if (same) return widths[w];
+    }
+    return -1;
+}
+// One block of 16 bf16 values -> fp16 in block order BITS, pairs 1 and 3 of every 8 stored values times sc_odd:
+// two 16-byte loads, the permutation in registers, two 16-byte stores.
+template <int BITS>
+__device__ __forceinline__ void convert_block16(const __nv_bfloat16* __restrict__ src, __half* __restrict__ dst, float sc_odd) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(src)), b = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float in[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        in[2 * i] = __uint_as_float(w[i] << 16);
+        in[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+    uint32_t o[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        const float sc = (q & 1) ? sc_odd : 1.f;
+        const __half2 h = __halves2half2(f32_to_f16_sat(in[order16<BITS>(2 * q)] * sc), f32_to_f16_sat(in[order16<BITS>(2 * q + 1)] * sc));
+        o[q] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    reinterpret_cast<uint4*>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    reinterpret_cast<uint4*>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
 
 
 template <int JMAX>
@@ -226,7 +269,7 @@ __global__ void __launch_bounds__(kRThreads)
 route_mma_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const __nv_bfloat16* __restrict__ Wr,
                  const float* __restrict__ logit_bias, int k, int norm, const __nv_bfloat16* __restrict__ w_sg,
                  int32_t* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ shared_gate,
-                 __half* __restrict__ x16, const Order16 order) {
+                 __half* __restrict__ x16, const Order16 order, const int obits) {
     constexpr int E = 32 * NT;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* s_x = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [2][kRT][kRPad]
@@ -333,7 +376,16 @@ route_mma_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const
             acc_g = warp_sum(acc_g);
             if (lane == 0) shared_gate[tok] = 1.0f / (1.0f + expf(-acc_g));
         }
-        if (x16 != nullptr) {
+        if (x16 != nullptr && obits >= 0) {
+            // a block of 16 per lane at a time, in the order the expert kernels of this code width read
+            __half* dst = x16 + (size_t)tok * H;
+            for (int c = lane * 16; c < H; c += 32 * 16) {
+                if (obits == 4) convert_block16<4>(xr + c, dst + c, order.pair_scale_odd);
+                else if (obits == 8) convert_block16<8>(xr + c, dst + c, order.pair_scale_odd);
+                else if (obits == 2) convert_block16<2>(xr + c, dst + c, order.pair_scale_odd);
+                else convert_block16<0>(xr + c, dst + c, order.pair_scale_odd);
+            }
+        } else if (x16 != nullptr) {
             __half2* dst = reinterpret_cast<__half2*>(x16 + (size_t)tok * H);
             for (int i = lane; i < H / 2; i += 32) {
                 const int blk = (2 * i) & ~15, p = (2 * i) & 15;
@@ -531,7 +583,8 @@ int launch_route_mma(const void* x, int n, int H, const void* Wr, const float* l
     IMX_CHECK_CUDA(cudaFuncSetAttribute(route_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     route_mma_kernel<NT><<<ceil_div(n, kRT), kRThreads, smem, stream>>>(
         (const __nv_bfloat16*)x, n, H, (const __nv_bfloat16*)Wr, logit_bias, k, norm, (const __nv_bfloat16*)w_sg,
-        topk_idx, topk_w, shared_gate, (__half*)x16, order); IMX_LAUNCHED();
+        topk_idx, topk_w, shared_gate, (__half*)x16, order,
+        ((uintptr_t)x % 16 == 0 && (uintptr_t)x16 % 16 == 0) ? order_bits(order) : -1); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }
