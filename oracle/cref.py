@@ -83,6 +83,11 @@ def prepare(x, p: O.MoEParams):
     return run, out
 
 
+def set_bf16_logits(on: bool) -> None:
+    """Router in the reference's dtypes (see oracle.moe.route(bf16_logits=True)); process-wide, off by default."""
+    lib().moe_ref_set_bf16_logits(C.c_int(1 if on else 0))
+
+
 def moe_forward(x, p: O.MoEParams):
     run, out = prepare(x, p)
     return run()

@@ -112,16 +112,40 @@ def softmax_rows(z) -> np.ndarray:
     return (e / e.sum(-1, keepdims=True)).astype(np.float32)
 
 
-def route(x, router_w, k: int, norm_topk_prob: bool = True, logit_bias=None):
+def route(x, router_w, k: int, norm_topk_prob: bool = True, logit_bias=None, bf16_logits: bool = False):
     """-> (top_idx int32 [N,k] descending by probability, lower expert index
-    first among exact ties; top_w fp32 [N,k]; probs fp32 [N,E])."""
-    probs = softmax_rows(router_logits(x, router_w, logit_bias))
+    first among exact ties; top_w fp32 [N,k]; probs fp32 [N,E]).
+
+    bf16_logits=True follows the reference's dtypes literally: its gate `Linear`
+    returns the logits in the activation dtype (bf16, linear.rs:170-177) and
+    softmax / argsort / topk run on bf16 arrays (moe.rs:67-74), so logits and
+    probabilities are rounded to bf16 before the selection.  The default keeps
+    both in fp32, which is what the kernels do; `routing_changes` counts the rows
+    where the two differ."""
+    z = router_logits(x, router_w, logit_bias)
+    if bf16_logits:
+        z = _r(z, True)
+    probs = softmax_rows(z)
+    if bf16_logits:
+        probs = _r(probs, True)
     order = np.argsort(-probs, axis=-1, kind="stable")        # moe.rs:71-72
     top_idx = order[:, :k].astype(np.int32)                    # moe.rs:73
     top_w = np.take_along_axis(probs, top_idx, axis=-1)        # moe.rs:74 (paired by expert)
     if norm_topk_prob:                                         # moe.rs:77-82
         top_w = (top_w.astype(np.float64) / top_w.astype(np.float64).sum(-1, keepdims=True))
     return top_idx, top_w.astype(np.float32), probs
+
+
+def routing_changes(x, router_w, k: int, logit_bias=None) -> dict:
+    """How much the bf16 rounding of logits and probabilities (the reference's
+    dtypes) changes the routing against fp32: rows whose expert SET differs,
+    rows whose ordered list differs, and assignments that go to another expert."""
+    a, _, _ = route(x, router_w, k, True, logit_bias, bf16_logits=False)
+    b, _, _ = route(x, router_w, k, True, logit_bias, bf16_logits=True)
+    set_rows = sum(1 for i in range(a.shape[0]) if set(a[i].tolist()) != set(b[i].tolist()))
+    moved = sum(len(set(a[i].tolist()) - set(b[i].tolist())) for i in range(a.shape[0]))
+    return {"rows": int(a.shape[0]), "rows_set_differs": int(set_rows),
+            "rows_order_differs": int((a != b).any(-1).sum()), "assignments_moved": int(moved)}
 
 
 def routing_margin(probs: np.ndarray, k: int) -> np.ndarray:

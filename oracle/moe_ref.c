@@ -101,6 +101,19 @@ static void swiglu(const float* x, int m, int H, int I, const ref_q* gate, size_
     qmm_t(g, m, down, down_row0, H, I, mode, bits, group, d, wrow);
 }
 
+/* Router in the reference's dtypes (logits and probabilities rounded to bf16 before the selection,
+ * moe.rs:67-74 with a bf16 model) instead of fp32; off by default.  Process-wide. */
+static int g_bf16_logits = 0;
+void moe_ref_set_bf16_logits(int on) { g_bf16_logits = on != 0; }
+static inline float round_bf16(float v) {
+    uint32_t u;
+    memcpy(&u, &v, 4);
+    if ((u & 0x7f800000u) != 0x7f800000u) u += 0x7fffu + ((u >> 16) & 1u);   /* to nearest, ties to even */
+    u &= 0xffff0000u;
+    memcpy(&v, &u, 4);
+    return v;
+}
+
 int moe_ref_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
@@ -131,11 +144,15 @@ int moe_ref_forward(int N, int H, int E, int k, int I, int Is, int norm, int mod
                 double acc = 0;
                 for (int c = 0; c < H; ++c) acc += (double)x[(size_t)t * H + c] * wr[c];
                 p[e] = (float)(acc + (logit_bias ? logit_bias[e] : 0.f));
+                if (g_bf16_logits) p[e] = round_bf16(p[e]);
                 if (p[e] > mx) mx = p[e];
             }
             double sum = 0;
             for (int e = 0; e < E; ++e) sum += exp((double)(p[e] - mx));
-            for (int e = 0; e < E; ++e) p[e] = (float)(exp((double)(p[e] - mx)) / sum);
+            for (int e = 0; e < E; ++e) {
+                p[e] = (float)(exp((double)(p[e] - mx)) / sum);
+                if (g_bf16_logits) p[e] = round_bf16(p[e]);
+            }
             double wsum = 0;
             for (int s = 0; s < k; ++s) {
                 int best = -1;
