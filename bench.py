@@ -48,8 +48,9 @@ sys.path.insert(0, ROOT)
 METRIC = "moe_layer_tokens_per_sec"
 UNIT = "tokens/s"
 # DRAM read + write of one launch of the decode gate/up kernel per expert it touches, from the ncu capture of a
-# 97-expert case (118.0 MB, profiles/decode_tmap_kernel_c2.md); each touched expert's bytes are read exactly once
-DECODE_GU_TRAFFIC_PER_EXPERT = 118.0e6 / 97
+# 97-expert case (113.9 MB read + 4.2 MB written, profiles/decode_kernels_c2.md); each touched expert's bytes are
+# read exactly once
+DECODE_GU_TRAFFIC_PER_EXPERT = 118.1e6 / 97
 
 
 def parse():
@@ -341,6 +342,13 @@ def single_gpu(args, dev, barrier):
         stage = np.zeros(5)
         reps = 30
         for _ in range(reps):
+            # the device is kept busy for ~0.1 ms while the call's launches and event records queue up behind it,
+            # so that the events bracket what the kernels take on the device, not the host's launch pace
+            # (the timed step is a graph replay: its kernels never wait for the host either)
+            try:
+                torch.cuda._sleep(200000)
+            except Exception:
+                pass
             _, st = moe.forward_timed(x)
             stage += np.array(st)
         out["stage"] = stage / reps
@@ -377,13 +385,14 @@ def single_gpu(args, dev, barrier):
         total_bytes = algorithmic_bytes_decode(cfg, touched)
         tmap = cfg.mode == "affine" and cfg.bits == 4 and cfg.group_size == 64
         line["roofline"] = {
-            "bound": "hbm", "kernel": "decode_tmap_kernel<true> (gate/up + SwiGLU)" if tmap else "decode kernel, first product",
+            "bound": "hbm", "kernel": "decode_first_kernel (gate/up + SwiGLU)" if tmap else "decode kernel, first product",
             "achieved": achieved, "peak": hbm_peak, "peak_source": f"of {which}", "unit": "GB/s", "frac": achieved / hbm_peak,
             "traffic": DECODE_GU_TRAFFIC_PER_EXPERT * (touched + 1) if tmap and cfg.name == "c2" else None,
             "traffic_note": "dram read + write per touched expert from the ncu capture of a 97-expert case "
-                            "(profiles/decode_tmap_kernel_c2.md), times the experts this launch touches: each expert's "
+                            "(profiles/decode_kernels_c2.md), times the experts this launch touches: each expert's "
                             "bytes are read once, so traffic grows in proportion",
             "algorithmic_bytes_per_launch": gu_bytes, "launch_ms": float(stage[2]), "stage_ms": stage_ms,
+            "launch_ms_note": "mean of 30 plain launches, CUDA events on the launching stream, launches queued ahead of the device",
             "layer": {"algorithmic_bytes": total_bytes, "touched_experts": touched,
                       "achieved_gbs": total_bytes / (m["ms"] * 1e-3) / 1e9,
                       "frac": total_bytes / (m["ms"] * 1e-3) / 1e9 / hbm_peak},
@@ -423,6 +432,8 @@ def tensor_roofline(cfg, stage, stage_ms, ms, tf_peak, which):
         "achieved": achieved, "peak": tf_peak, "peak_source": f"of {which} (bf16 burst)", "unit": "TFLOP/s",
         "frac": achieved / tf_peak, "traffic": None, "algorithmic_flops_per_launch": gu_flops,
         "launch_ms": float(stage[2]), "stage_ms": stage_ms,
+        "launch_ms_note": "mean of 30 plain launches, CUDA events on the launching stream, launches queued ahead of the device; "
+                          "the stage includes the slot-order gather that precedes the first product",
         "layer": {"algorithmic_flops": total_flops, "achieved_tflops": total_flops / (ms * 1e-3) / 1e12,
                   "frac": total_flops / (ms * 1e-3) / 1e12 / tf_peak},
     }
