@@ -617,6 +617,17 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # A collective that never returns (a rank that died, a fabric problem) must not hold the ranks for ever:
+        # after ten minutes the process says where it was and leaves.
+        import threading
+
+        def give_up():
+            print(f"[bench] rank {rank}: no result after 600 s, leaving", file=sys.stderr, flush=True)
+            os._exit(4)
+
+        watchdog = threading.Timer(600.0, give_up)
+        watchdog.daemon = True
+        watchdog.start()
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
