@@ -284,8 +284,10 @@ IMX_API int imx_gather_rows(const void* src, const int32_t* index, int n_rows, s
 typedef struct imx_ep_ctx imx_ep_ctx;
 
 #define IMX_EP_UNIQUE_ID_BYTES 128
-#define IMX_EP_AUTO 0        /* gathered up to 1023 tokens over all ranks, else all-to-all */
-#define IMX_EP_GATHERED 1    /* all-gather tokens, local experts, reduce-scatter fp32 partial sums: fixed shapes,
+#define IMX_EP_AUTO 0        /* gathered up to 1023 tokens over all ranks; beyond that the schedule that moves fewer
+                                bytes: gathered while 2 * top_k >= 3 * ranks, else all-to-all */
+#define IMX_EP_GATHERED 1    /* all-gather tokens, every rank routes all of them and runs its own experts (decode or
+                                tensor-core kernels by batch size), reduce-scatter of fp32 partial rows: fixed shapes,
                                 no host synchronisation (can be captured in a CUDA graph) */
 #define IMX_EP_ALL_TO_ALL 2  /* dispatch / return of fp16 rows by grouped ncclSend / ncclRecv; one host
                                 synchronisation per call (the exchange's split sizes); results are bit-identical to

@@ -137,10 +137,12 @@ __global__ void gather_rows_kernel(const uint32_t* __restrict__ src, const int32
 constexpr int kGatherWarps = 8;
 __global__ void __launch_bounds__(kGatherWarps * 32)
 gather_rows16_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ index, int n_rows, int pieces,
-                     uint4* __restrict__ dst) {
+                     uint4* __restrict__ dst, const int32_t* __restrict__ skip_from_dev, int skip_to) {
     const int lane = threadIdx.x & 31;
     const int stride = gridDim.x * kGatherWarps;
+    const int skip_from = skip_from_dev != nullptr ? __ldg(skip_from_dev) : n_rows;   // rows [skip_from, skip_to) are nobody's
     for (int j = blockIdx.x * kGatherWarps + (threadIdx.x >> 5); j < n_rows; j += stride) {
+        if (j >= skip_from && j < skip_to) continue;
         const uint4* s = src + (size_t)__ldg(index + j) * pieces;
         uint4* d = dst + (size_t)j * pieces;
         for (int i0 = lane; i0 < pieces; i0 += 32 * 8) {
@@ -158,7 +160,7 @@ gather_rows16_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ 
 }  // namespace
 
 int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const int32_t* skip_from_dev, int skip_to) {
     IMX_REQUIRE(row_bytes % 4 == 0 && row_bytes > 0, "gather_rows: row size (%zu) must be a positive multiple of 4", row_bytes);
     IMX_REQUIRE(row_bytes % 16 != 0 || (((uintptr_t)src | (uintptr_t)dst) % 16) == 0,
                 "gather_rows: 16-byte rows need 16-byte aligned buffers");
@@ -168,10 +170,11 @@ int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t
         int grid = ceil_div(n_rows, kGatherWarps);
         if (grid > 148 * 8) grid = 148 * 8;
         gather_rows16_kernel<<<grid, kGatherWarps * 32, 0, stream>>>((const uint4*)src, index, n_rows, (int)(row_bytes / 16),
-                                                                    (uint4*)dst); IMX_LAUNCHED();
+                                                                    (uint4*)dst, skip_from_dev, skip_to); IMX_LAUNCHED();
         IMX_CHECK_CUDA(cudaGetLastError());
         return IMX_OK;
     }
+    IMX_REQUIRE(skip_from_dev == nullptr, "gather_rows: a skipped range needs rows that are multiples of 16 bytes");
     const int threads = words >= 1024 ? 256 : (words >= 128 ? 128 : 32);
     gather_rows_kernel<<<n_rows, threads, 0, stream>>>((const uint32_t*)src, index, words, (uint32_t*)dst); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
@@ -186,8 +189,8 @@ int launch_combine(const void* rows, const float* row_scale, const int32_t* inv_
     if (n == 0) return IMX_OK;
     dim3 grid(n, ceil_div(H, kCCols * (rows_f16 ? 2 : 1)));
     const __nv_bfloat16* res = (const __nv_bfloat16*)residual;
-    IMX_REQUIRE(!(rows_f16 && f32_out), "combine: fp16 rows with fp32 output is not a supported combination");
-    if (rows_f16) combine_kernel<false, true><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res, shared_scale);
+    if (rows_f16 && f32_out) combine_kernel<true, true><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res, shared_scale);
+    else if (rows_f16) combine_kernel<false, true><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res, shared_scale);
     else if (f32_out) combine_kernel<true, false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res, shared_scale);
     else combine_kernel<false, false><<<grid, kCThreads, 0, stream>>>(rows, row_scale, inv_perm, k, H, shared_rows, y, res, shared_scale); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());

@@ -184,6 +184,27 @@ ep_regroup_kernel(const int32_t* __restrict__ counts, int R, int E, int e_lo, in
     }
 }
 
+// Gathered schedule, last step: y = bf16(sum over the ranks of a token's partial row + gate * shared-expert row).
+__global__ void finish_rows_kernel(const float* __restrict__ mine, const __half* __restrict__ shared, const float* __restrict__ gate,
+                                   int H, __nv_bfloat16* __restrict__ y) {
+    const size_t t = blockIdx.x;
+    const float g = gate != nullptr ? gate[t] : 1.f;
+    for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+        float4 v = *reinterpret_cast<const float4*>(mine + t * H + c);
+        if (shared != nullptr) {
+            const uint2 q = *reinterpret_cast<const uint2*>(shared + t * H + c);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&q.x));
+            const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&q.y));
+            v.x += a.x * g; v.y += a.y * g; v.z += b.x * g; v.w += b.y * g;
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(y + t * H + c) = o;
+    }
+}
+
 struct Common {
     int32_t* status;
     SchedWs sw;
@@ -214,6 +235,7 @@ struct GatherWs {
     void* sort_scratch;
     size_t sort_scratch_bytes;
     __half* act;
+    __half* xs;           // activations in slot order (tensor-core kernels: batches with >= 32 rows per local expert)
     float* rows;
     float* psum;
     float* partial;
@@ -257,6 +279,7 @@ GatherWs carve_gather(const imx_ep_ctx& x, int n, void* base) {
     w.sort_scratch = cv.take<uint8_t>(w.sort_scratch_bytes);
     w.act_stride = c.intermediate > c.shared_intermediate ? c.intermediate : c.shared_intermediate;
     w.act = cv.take<__half>((size_t)(A + ns) * w.act_stride);
+    if ((long)A / x.world >= 32L * x.e_loc) w.xs = cv.take<__half>((size_t)(A + ns) * c.hidden);
     w.rows = cv.take<float>((size_t)(A + ns) * c.hidden);
     w.psum = cv.take<float>((size_t)(A + ns) * (w.act_stride / 16 + 1));
     w.partial = cv.take<float>((size_t)nA * c.hidden);
@@ -363,11 +386,12 @@ int forward_gathered(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, i
     IMX_TRY(make_expert_set(cl, f, w->gate_up, w->down, x.e_loc, has_shared ? w : nullptr, &set));
     int path;
     IMX_TRY(pick_path(cl, set, (long)A / R, &path));
-    if (is_prefill(path)) {      // this schedule sums fp32 rows across ranks: the tensor-core path's fp16 rows go the other way
+    if (is_prefill(path) && ws.xs == nullptr) {      // (cannot happen: the workspace has the buffer at these sizes)
         imx_moe_config cd = cl;
         cd.path = IMX_PATH_DECODE;
         if (pick_path(cd, set, (long)A / R, &path) != IMX_OK) path = IMX_PATH_GENERIC;
     }
+    const bool tc = is_prefill(path);                // tensor-core kernels: fp16 rows, routing weight applied in the combine
     const bool tmap_decode = path == IMX_PATH_DECODE && decode_tmap_supported(set);
 
     IMX_CHECK_NCCL(nc->AllGather(xin, ws.xg, (size_t)n * c.hidden, ncclBfloat16, x.comm, stream));
@@ -400,6 +424,9 @@ int forward_gathered(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, i
     ga.set = set;
     ga.in = ws.x16;
     ga.row_index = ws.tok_of_slot;
+    ga.xs = ws.xs;
+    ga.slots_end_dev = ws.offsets + x.e_loc;         // the sorted slots end where the local experts' rows end ...
+    ga.slots_resume = A;                             // ... and the shared expert's slots follow the A assignment slots
     ga.n_slots = A + (has_shared ? n : 0);
     ga.units = ws.units;
     ga.n_units = ws.c.n_units;
@@ -412,15 +439,25 @@ int forward_gathered(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, i
     ga.gsum_x_ready = sums_done ? 1 : 0;
     ga.act = ws.act;
     ga.act_stride = ws.act_stride;
-    ga.row_scale = ws.w_of_slot;
+    ga.row_scale = tc ? nullptr : ws.w_of_slot;
     ga.out = ws.rows;
+    ga.out16 = tc ? reinterpret_cast<__half*>(ws.rows) : nullptr;
     ga.status = ws.c.status;
     IMX_TRY(run_experts(path, ga, stream));
     // fp32 partial sums over the local experts, for all tokens (dropped assignments contribute nothing)
-    IMX_TRY(launch_combine(ws.rows, nullptr, ws.inv_perm, nA, c.top_k, c.hidden, nullptr, ws.partial, stream, true));
+    IMX_TRY(launch_combine(ws.rows, tc ? ws.w_of_slot : nullptr, ws.inv_perm, nA, c.top_k, c.hidden, nullptr, ws.partial, stream, true,
+                           nullptr, tc));
     IMX_CHECK_NCCL(nc->ReduceScatter(ws.partial, ws.mine, (size_t)n * c.hidden, ncclFloat, ncclSum, x.comm, stream));
-    IMX_TRY(launch_combine(ws.mine, nullptr, ws.ident, n, 1, c.hidden, has_shared ? ws.rows + (size_t)A * c.hidden : nullptr, y,
-                           stream));
+    if (tc) {
+        // the shared expert's rows of the local tokens are fp16 and ungated on this path
+        finish_rows_kernel<<<n, 256, 0, stream>>>(ws.mine, has_shared ? reinterpret_cast<const __half*>(ws.rows) + (size_t)A * c.hidden : nullptr,
+                                                 has_shared ? ws.shared_gate + (size_t)x.rank * n : nullptr, c.hidden,
+                                                 (__nv_bfloat16*)y); IMX_LAUNCHED();
+        IMX_CHECK_CUDA(cudaGetLastError());
+    } else {
+        IMX_TRY(launch_combine(ws.mine, nullptr, ws.ident, n, 1, c.hidden, has_shared ? ws.rows + (size_t)A * c.hidden : nullptr, y,
+                               stream));
+    }
     if (info != nullptr) {
         info->schedule = IMX_EP_GATHERED;
         info->rows_received = -1;
@@ -601,9 +638,13 @@ int forward_a2a(imx_ep_ctx& x, const imx_moe_weights* w, const void* xin, int n,
 
 int pick_schedule(const imx_ep_ctx& x, int n, int schedule) {
     if (schedule != IMX_EP_AUTO) return schedule;
-    // decode-size batches: fixed shapes and no host round trip; beyond that the rows of a token go only where its
-    // experts live
-    return (long)n * x.world <= 1023 ? IMX_EP_GATHERED : IMX_EP_ALL_TO_ALL;
+    // Decode-size batches: fixed shapes and no host round trip.  Beyond that, whichever moves fewer bytes: the
+    // gathered schedule sends a token's bf16 row out and its fp32 partial row back once per other rank,
+    // (R - 1) * 6 * H bytes; the all-to-all schedule sends the fp16 rows of its k assignments both ways,
+    // 2 * k * (R - 1) / R * 2 * H bytes -- fewer from 2 k < 3 R on (top-8: eight ranks and more).
+    if ((long)n * x.world <= 1023) return IMX_EP_GATHERED;
+    if ((long)n * x.world * x.cfg.top_k > (1L << 24)) return IMX_EP_ALL_TO_ALL;
+    return 2 * x.cfg.top_k >= 3 * x.world ? IMX_EP_GATHERED : IMX_EP_ALL_TO_ALL;
 }
 
 }  // namespace

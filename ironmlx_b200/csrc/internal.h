@@ -136,6 +136,8 @@ struct GroupedArgs {
     const int32_t* out_index;      // prefill path only: output row of each slot (nullptr: the slot itself)
     int32_t* status;               // device status word
     int second_only;               // run the second product alone: out = act . down^T (a plain quantized matmul)
+    const int32_t* slots_end_dev;  // prefill path, optional: slots [*slots_end_dev, slots_resume) hold nothing (expert
+    int slots_resume;              // parallelism: assignments of other ranks' experts); the gather skips them
 };
 
 bool decode_mma_supported(const ExpertSet& s);
@@ -183,8 +185,10 @@ int launch_combine(const void* rows, const float* row_scale, const int32_t* inv_
 // (shared_scale: per-token factor of the shared rows when they arrive ungated; nullptr: already gated)
 // y = w * T(x * rsqrt(mean(x^2) + eps)) per row (y may be null), inv_out[row] = the factor (may be null).
 int launch_rms_norm(const void* x, int n, int H, const void* w, float eps, void* y, float* inv_out, cudaStream_t stream);
+// dst[j, :] = src[index[j], :]; rows [*skip_from_dev, skip_to) are left alone when skip_from_dev is given
+// (slots no expert of this rank owns).
 int launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,
-                       cudaStream_t stream);
+                       cudaStream_t stream, const int32_t* skip_from_dev = nullptr, int skip_to = 0);
 
 // Builds the unit list for a caller-given offsets array (stage-level API).  extra_from >= 0: the units of that
 // (last) expert are listed as the extra expert's.

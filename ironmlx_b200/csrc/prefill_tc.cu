@@ -1068,7 +1068,7 @@ int launch_prefill_tc(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid
     // activations in sorted-slot order (the `take_axis` of moe.rs:124-127, once for all experts)
     const __half* xsrc = a.in;                     // already slot-ordered when there is no row index
     if (a.row_index != nullptr && !a.second_only) {
-        IMX_TRY(launch_gather_rows(a.in, a.row_index, a.n_slots, (size_t)s.n_in * 2, a.xs, stream));
+        IMX_TRY(launch_gather_rows(a.in, a.row_index, a.n_slots, (size_t)s.n_in * 2, a.xs, stream, a.slots_end_dev, a.slots_resume));
         xsrc = a.xs;
     }
     TcMaps mgu, mdn;

@@ -58,15 +58,17 @@ def _worker(rank, world, port, out):
         cabi = ep.ExpertParallel(local, *args)
         staged = ep.ExpertParallelMoE(ep.CudaStages(dev), local, *args)
         res = {}
-        for mode, n in (("gathered", CFG.tokens), ("a2a", TOKENS_A2A)):
+        # "gathered_tc": the gathered schedule at a prefill-size batch, where it runs the tensor-core expert kernels
+        for mode, n in (("gathered", CFG.tokens), ("a2a", TOKENS_A2A), ("gathered_tc", TOKENS_A2A)):
             x = wl.activations(tokens=n, block=rank)
             xd = t_bf16(x, dev)
             y = None
+            schedule = "gathered" if mode == "gathered_tc" else mode
             for _ in range(2):                              # twice: the workspace is left clean
-                y = cabi.forward(xd, schedule=mode)
+                y = cabi.forward(xd, schedule=schedule)
             torch.cuda.synchronize()
             cabi.check_status()
-            ys = staged.forward(xd, mode=mode)
+            ys = staged.forward(xd, mode=schedule)
             torch.cuda.synchronize()
             y1, tr = single.forward_with_stream(xd, trace=True)
             torch.cuda.synchronize()
@@ -91,10 +93,12 @@ def test_ep_matches_single_gpu_and_checker(cuda, world):
     out = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     for rank in range(world):
-        for mode in ("gathered", "a2a"):
+        for mode in ("gathered", "a2a", "gathered_tc"):
             r = out[rank][mode]
             assert r["perm_ok"] and r["err_ref"] <= 2e-3, (rank, mode, r)
             assert r["err_staged"] <= 1.5e-3, (rank, mode, r)   # the Python exchange over the stage-level calls (fp32 rows)
+        # the tensor-core kernels behind the gathered schedule: the single-GPU path's fp16 rows, summed per rank in fp32
+        assert out[rank]["gathered_tc"]["err_single"] <= 5e-4, (rank, out[rank]["gathered_tc"])
         # the all-to-all schedule moves the single-GPU path's own fp16 rows and sums them in the same order
         assert out[rank]["a2a"]["same_as_single"], (rank, out[rank]["a2a"])
         # fp32 partial sums cross ranks in the collective's order: same values up to summation order
