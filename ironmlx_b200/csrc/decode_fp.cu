@@ -38,7 +38,10 @@ using namespace decode;
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kStages = 4;          // register prefetch depth (iterations of 128 values)
+// Two CTAs of eight warps per SM with a ring of two iterations each (128 registers): measured against one CTA with
+// four iterations in flight (238 registers), c4 decode: 441 -> 389 us (mxfp8), 284 -> 219 us (nvfp4) per step.
+constexpr int kStages = 2;          // register prefetch depth (iterations of 128 values)
+constexpr int kCtasPerSm = 2;
 
 // MX = true: mxfp8, else nvfp4.
 template <bool MX>
@@ -292,7 +295,7 @@ __device__ __forceinline__ void finish(const GroupedArgs& a, const FpTask& c, fl
 }
 
 template <bool MX, bool SWIGLU>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 decode_fp_kernel(const GroupedArgs a, const int pairs_per_unit) {
     const int lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -367,11 +370,11 @@ int launch_mode(const GroupedArgs& a, cudaStream_t stream, cudaEvent_t mid) {
     IMX_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int mid_max = s.has_extra && s.x_mid > s.n_mid ? s.x_mid : s.n_mid;
     if (!a.second_only) {
-        decode_fp_kernel<MX, true><<<sms, kThreads, 0, stream>>>(a, mid_max / 16); IMX_LAUNCHED();
+        decode_fp_kernel<MX, true><<<sms * kCtasPerSm, kThreads, 0, stream>>>(a, mid_max / 16); IMX_LAUNCHED();
         IMX_CHECK_CUDA(cudaGetLastError());
     }
     if (mid) IMX_CHECK_CUDA(cudaEventRecord(mid, stream));
-    decode_fp_kernel<MX, false><<<sms, kThreads, 0, stream>>>(a, s.n_in / 32); IMX_LAUNCHED();
+    decode_fp_kernel<MX, false><<<sms * kCtasPerSm, kThreads, 0, stream>>>(a, s.n_in / 32); IMX_LAUNCHED();
     IMX_CHECK_CUDA(cudaGetLastError());
     return IMX_OK;
 }
