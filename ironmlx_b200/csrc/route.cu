@@ -250,12 +250,14 @@ route_kernel(const __nv_bfloat16* __restrict__ x, int H, const __nv_bfloat16* __
 // 32 tokens x all experts per CTA with mma.sync m16n8k16 (bf16 x bf16 -> fp32):
 // activations and router rows stream through shared memory in K chunks of 64
 // (16-byte cp.async, double buffered), the fp32 logits of the tile land in
-// shared memory and each warp finishes 8 tokens with the same warp
-// softmax/top-k as the decode-size kernel.
+// shared memory and each warp finishes its share of the tokens with the same
+// warp softmax/top-k as the decode-size kernel.  W warps per CTA: each takes
+// E / W experts of the product and 32 / W tokens of the epilogue (eight warps
+// from 64 experts on: the epilogue is half of the kernel's time and serial per
+// warp).
 constexpr int kRT = 32;            // tokens per CTA
 constexpr int kRK = 64;            // K chunk
 constexpr int kRPad = 72;          // bf16 per smem row (64 + 8: conflict-free fragment loads)
-constexpr int kRThreads = 128;
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -264,13 +266,16 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT>   // n-tiles of 8 experts per warp: E = 32 * NT
-__global__ void __launch_bounds__(kRThreads)
+template <int NT, int W>   // E = 32 * NT experts, W warps
+__global__ void __launch_bounds__(W * 32)
 route_mma_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const __nv_bfloat16* __restrict__ Wr,
                  const float* __restrict__ logit_bias, int k, int norm, const __nv_bfloat16* __restrict__ w_sg,
                  int32_t* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ shared_gate,
                  __half* __restrict__ x16, const Order16 order, const int obits) {
     constexpr int E = 32 * NT;
+    constexpr int kRThreads = W * 32;
+    constexpr int NW = 4 * NT / W;            // n-tiles of 8 experts per warp
+    static_assert(NW >= 1 && NW * W == 4 * NT, "experts must divide evenly over the warps");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* s_x = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [2][kRT][kRPad]
     __nv_bfloat16* s_w = s_x + 2 * kRT * kRPad;                                      // [2][E][kRPad]
@@ -297,11 +302,11 @@ route_mma_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
-    float acc[2][NT][4];
+    float acc[2][NW][4];
 #pragma unroll
     for (int m = 0; m < 2; ++m)
 #pragma unroll
-        for (int n = 0; n < NT; ++n)
+        for (int n = 0; n < NW; ++n)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
 
@@ -317,7 +322,7 @@ route_mma_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const
         }
         __syncthreads();
         const __nv_bfloat16* xs = s_x + buf * kRT * kRPad;
-        const __nv_bfloat16* ws = s_w + (buf * E + warp * (8 * NT)) * kRPad;
+        const __nv_bfloat16* ws = s_w + (buf * E + warp * (8 * NW)) * kRPad;
 #pragma unroll
         for (int kk = 0; kk < kRK / 16; ++kk) {
             uint32_t af[2][4];
@@ -330,7 +335,7 @@ route_mma_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const
                 af[m][3] = *reinterpret_cast<const uint32_t*>(p + 8 * kRPad + 8);
             }
 #pragma unroll
-            for (int n = 0; n < NT; ++n) {
+            for (int n = 0; n < NW; ++n) {
                 const __nv_bfloat16* p = ws + (n * 8 + g) * kRPad + kk * 16 + 2 * t;
                 const uint32_t b0 = *reinterpret_cast<const uint32_t*>(p);
                 const uint32_t b1 = *reinterpret_cast<const uint32_t*>(p + 8);
@@ -344,8 +349,8 @@ route_mma_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const
 #pragma unroll
     for (int m = 0; m < 2; ++m)
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
-            const int e = warp * (8 * NT) + n * 8 + 2 * t;
+        for (int n = 0; n < NW; ++n) {
+            const int e = warp * (8 * NW) + n * 8 + 2 * t;
             const float b0 = logit_bias ? logit_bias[e] : 0.f, b1 = logit_bias ? logit_bias[e + 1] : 0.f;
             s_logits[(m * 16 + g) * E + e] = acc[m][n][0] + b0;
             s_logits[(m * 16 + g) * E + e + 1] = acc[m][n][1] + b1;
@@ -353,8 +358,8 @@ route_mma_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int H, const
             s_logits[(m * 16 + g + 8) * E + e + 1] = acc[m][n][3] + b1;
         }
     __syncthreads();
-    // each warp finishes 8 tokens: softmax/top-k, shared gate, fp16 copy
-    for (int r = warp * 8; r < warp * 8 + 8; ++r) {
+    // each warp finishes its tokens: softmax/top-k, shared gate, fp16 copy
+    for (int r = warp * (kRT / W); r < (warp + 1) * (kRT / W); ++r) {
         const int tok = tok0 + r;
         if (tok >= n_tokens) break;
         softmax_topk_warp<NT>(s_logits + r * E, E, k, norm, topk_idx + (size_t)tok * k, topk_w + (size_t)tok * k);
@@ -580,8 +585,9 @@ int launch_route_mma(const void* x, int n, int H, const void* Wr, const float* l
     const size_t stage = (size_t)2 * (kRT + E) * kRPad * sizeof(__nv_bfloat16);
     const size_t logits = (size_t)kRT * E * sizeof(float);
     const size_t smem = stage > logits ? stage : logits;
-    IMX_CHECK_CUDA(cudaFuncSetAttribute(route_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    route_mma_kernel<NT><<<ceil_div(n, kRT), kRThreads, smem, stream>>>(
+    constexpr int W = NT >= 2 ? 8 : 4;
+    IMX_CHECK_CUDA(cudaFuncSetAttribute(route_mma_kernel<NT, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    route_mma_kernel<NT, W><<<ceil_div(n, kRT), W * 32, smem, stream>>>(
         (const __nv_bfloat16*)x, n, H, (const __nv_bfloat16*)Wr, logit_bias, k, norm, (const __nv_bfloat16*)w_sg,
         topk_idx, topk_w, shared_gate, (__half*)x16, order,
         ((uintptr_t)x % 16 == 0 && (uintptr_t)x16 % 16 == 0) ? order_bits(order) : -1); IMX_LAUNCHED();
