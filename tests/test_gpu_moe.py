@@ -266,6 +266,10 @@ def test_prefill_shape_reduced(cuda, group):
     MoEConfig("tm-wide-shared", 12, 1024, 8, 2, 512, 1536, seed=34),
     MoEConfig("tm-crowded", 100, 512, 2, 2, 512, 512, seed=35),          # 100 rows per expert: many units
     MoEConfig("tm-k-eq-e", 9, 512, 4, 4, 512, 1024, seed=36),
+    # a long second reduction: its tile pairs go out as chunks of four stages and the chunk that arrives last adds
+    # the parts up
+    MoEConfig("tm-long-mid", 20, 512, 4, 2, 2048, 2048, seed=38),
+    MoEConfig("tm-long-mid-ragged", 37, 1024, 8, 3, 2048, 512, seed=39),
 ], ids=lambda c: c.name)
 def test_decode_tensor_map_kernel(cuda, cfg):
     """Shapes the tensor-map fed decode kernel takes (4-bit, group 64, sizes % 512 == 0): against the
