@@ -25,6 +25,7 @@ def _qlinear(out_dim, in_dim, mode, bits, group, seed):
 @pytest.mark.parametrize("mode,bits,group", [("affine", 4, 64), ("affine", 8, 64), ("affine", 2, 64), ("mxfp8", 8, 32),
                                              ("nvfp4", 4, 16)])
 @pytest.mark.parametrize("m,in_dim,out_dim", [(1, 2048, 512), (8, 512, 2048), (40, 1024, 1024), (300, 2048, 512),
+                                              (70, 512, 20480),        # a vocabulary-sized output on the tensor-core kernel
                                               (5, 192, 320)])          # the last shape: the scalar fallback
 def test_quantized_linear_forward(cuda, m, in_dim, out_dim, mode, bits, group):
     if in_dim % group:
