@@ -63,31 +63,45 @@ combine_kernel(const void* __restrict__ rows, const float* __restrict__ row_scal
     float acc[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = 0.f;
-    constexpr int kBatch = F16_ROWS ? 4 : 8;     // independent row loads in flight, added in order
+    // Eight independent 16-byte row loads in flight per thread, kept as they arrive (four registers each) and
+    // unpacked when they are added, in slot order.
+    constexpr int kBatch = 8;
     for (int s0 = 0; s0 < k; s0 += kBatch) {
-        float v[kBatch][V];
+        uint4 raw[kBatch];
         float w[kBatch];
 #pragma unroll
         for (int j = 0; j < kBatch; ++j) {
             const int slot = (s0 + j < k) ? s_slot[s0 + j] : -1;
+            raw[j] = make_uint4(0u, 0u, 0u, 0u);      // dropped assignment (moe.rs:100) or past the last slot: zeros
             if (slot >= 0) {
-                load_row<F16_ROWS>(rows, (size_t)slot * H + c, v[j]);
-            } else {                                  // dropped assignment (moe.rs:100) or past the last slot
-#pragma unroll
-                for (int i = 0; i < V; ++i) v[j][i] = 0.f;
+                const size_t idx = (size_t)slot * H + c;
+                raw[j] = F16_ROWS ? __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(rows) + idx))
+                                  : __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(rows) + idx));
             }
             w[j] = (slot >= 0 && row_scale != nullptr) ? __ldg(row_scale + slot) : 1.f;
         }
-        if (row_scale != nullptr) {
 #pragma unroll
-            for (int j = 0; j < kBatch; ++j)          // rows arrive unweighted: scale (one rounding), then add
+        for (int j = 0; j < kBatch; ++j) {
+            float v[V];
+            if (F16_ROWS) {
+                const uint32_t q[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
 #pragma unroll
-                for (int i = 0; i < V; ++i) acc[i] += v[j][i] * w[j];
-        } else {
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&q[e]));
+                    v[2 * e] = f.x;
+                    v[2 * e + 1] = f.y;
+                }
+            } else {
+                v[0] = __uint_as_float(raw[j].x); v[1] = __uint_as_float(raw[j].y);
+                v[2] = __uint_as_float(raw[j].z); v[3] = __uint_as_float(raw[j].w);
+            }
+            if (row_scale != nullptr) {               // rows arrive unweighted: scale (one rounding), then add
 #pragma unroll
-            for (int j = 0; j < kBatch; ++j)
+                for (int i = 0; i < V; ++i) acc[i] += v[i] * w[j];
+            } else {
 #pragma unroll
-                for (int i = 0; i < V; ++i) acc[i] += v[j][i];
+                for (int i = 0; i < V; ++i) acc[i] += v[i];
+            }
         }
     }
     if (shared_rows != nullptr) {
